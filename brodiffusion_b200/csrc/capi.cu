@@ -1,0 +1,318 @@
+// C-ABI layer: argument validation, tensor-map construction and kernel
+// dispatch.  No device memory is allocated here; every kernel runs on the
+// stream the caller passes.
+#include "../../include/bdattn.h"
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "sdpa_internal.h"
+#include "tc05.cuh"
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return -1;
+}
+
+int cuda_fail(const char* op, cudaError_t e) {
+    return fail("%s: CUDA error: %s", op, cudaGetErrorString(e));
+}
+
+// The current device must be a Blackwell data-centre part (sm_100): the
+// kernels are sm_100a-only and there is no other path.
+int require_sm100(const char* op) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    static thread_local int checked_dev = -1;
+    if (checked_dev == dev) return 0;
+    int major = 0, minor = 0;
+    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev);
+    if (major != 10) {
+        return fail("%s: device %d is sm_%d%d; this library only runs on sm_100 (B200) and has no "
+                    "other path", op, dev, major, minor);
+    }
+    checked_dev = dev;
+    return 0;
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) !=
+                cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            p = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+// (cols, rows, batch) row-major 16-bit tensor, box = 64 columns x box_rows rows,
+// 128-byte swizzle, zero fill outside the tensor.
+int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, long long cols,
+                long long rows, long long batch, long long ld, long long batch_stride,
+                int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail("%s: cuTensorMapEncodeTiled is not available from the driver", op);
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                          static_cast<cuuint64_t>(batch)};
+    if (batch_stride <= 0) batch_stride = rows * ld;
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
+    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        return fail("%s: cuTensorMapEncodeTiled failed (CUresult %d) for base=%p cols=%lld rows=%lld "
+                    "batch=%lld ld=%lld batch_stride=%lld", op, static_cast<int>(r), base, cols, rows,
+                    batch, ld, batch_stride);
+    }
+    return 0;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int bdattn_version(void) { return 100; }
+
+const char* bdattn_last_error(void) { return g_err; }
+
+int bdattn_device_status(int* status, int clear) {
+    if (status == nullptr) return fail("bdattn_device_status: status is null");
+    if (require_sm100("bdattn_device_status")) return -1;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return cuda_fail("bdattn_device_status", e);
+    int v = 0;
+    e = cudaMemcpyFromSymbol(&v, bdattn::g_device_status, sizeof(int));
+    if (e != cudaSuccess) return cuda_fail("bdattn_device_status", e);
+    *status = v;
+    if (clear && v != 0) {
+        int z = 0;
+        e = cudaMemcpyToSymbol(bdattn::g_device_status, &z, sizeof(int));
+        if (e != cudaSuccess) return cuda_fail("bdattn_device_status", e);
+    }
+    return 0;
+}
+
+int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
+    const char* op = "bdattn_sdpa_fwd";
+    if (p == nullptr) return fail("%s: params is null", op);
+    if (require_sm100(op)) return -1;
+    if (p->dtype != BDATTN_BF16 && p->dtype != BDATTN_F16)
+        return fail("%s: dtype must be BF16 or F16 (got %d)", op, p->dtype);
+    if (p->batch < 1 || p->num_heads < 1) return fail("%s: batch and num_heads must be >= 1", op);
+    const int hd = p->head_dim;
+    if (hd < 8 || hd > 256 || hd % 8 != 0)
+        return fail("%s: head_dim must be a multiple of 8 in [8, 256] (got %d)", op, hd);
+    if (p->n_q_seg < 1 || p->n_q_seg > 2 || p->n_kv_seg < 1 || p->n_kv_seg > 2)
+        return fail("%s: n_q_seg and n_kv_seg must be 1 or 2", op);
+    if (p->mask_mode != BDATTN_MASK_NONE && p->mask_mode != BDATTN_MASK_CAUSAL)
+        return fail("%s: unknown mask_mode %d", op, p->mask_mode);
+    const long long D = static_cast<long long>(p->num_heads) * hd;
+    long long Lq = 0, Lk = 0;
+    for (int s = 0; s < p->n_q_seg; ++s) {
+        if (p->q[s] == nullptr || p->o[s] == nullptr) return fail("%s: q/o segment %d is null", op, s);
+        if (p->q_rows[s] < 1) return fail("%s: q_rows[%d] must be >= 1", op, s);
+        if (p->q_ld[s] < D || p->o_ld[s] < D)
+            return fail("%s: q_ld/o_ld of segment %d smaller than num_heads*head_dim", op, s);
+        if (p->q_ld[s] % 8 || p->o_ld[s] % 8 || !aligned16(p->q[s]) || !aligned16(p->o[s]) ||
+            p->q_batch_stride[s] % 8 || p->o_batch_stride[s] % 8)
+            return fail("%s: q/o segment %d must be 16-byte aligned with strides that are multiples of 8 "
+                        "elements", op, s);
+        Lq += p->q_rows[s];
+    }
+    for (int s = 0; s < p->n_kv_seg; ++s) {
+        if (p->k[s] == nullptr || p->v[s] == nullptr) return fail("%s: k/v segment %d is null", op, s);
+        if (p->kv_rows[s] < 1) return fail("%s: kv_rows[%d] must be >= 1", op, s);
+        if (p->k_ld[s] < D || p->v_ld[s] < D)
+            return fail("%s: k_ld/v_ld of segment %d smaller than num_heads*head_dim", op, s);
+        if (p->k_ld[s] % 8 || p->v_ld[s] % 8 || !aligned16(p->k[s]) || !aligned16(p->v[s]) ||
+            p->k_batch_stride[s] % 8 || p->v_batch_stride[s] % 8)
+            return fail("%s: k/v segment %d must be 16-byte aligned with strides that are multiples of 8 "
+                        "elements", op, s);
+        Lk += p->kv_rows[s];
+    }
+    const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(hd));
+    const bool bf16 = p->dtype == BDATTN_BF16;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+    if (hd == 64 || hd == 128) {
+        bdattn::SdpaLaunch L;
+        std::memset(&L, 0, sizeof(L));
+        for (int s = 0; s < 2; ++s) {
+            const int qs = s < p->n_q_seg ? s : 0;
+            const int ks = s < p->n_kv_seg ? s : 0;
+            if (make_map_3d(op, &L.tmQ[s], p->q[qs], bf16, D, p->q_rows[qs], p->batch, p->q_ld[qs],
+                            p->q_batch_stride[qs], 128))
+                return -1;
+            if (make_map_3d(op, &L.tmK[s], p->k[ks], bf16, D, p->kv_rows[ks], p->batch, p->k_ld[ks],
+                            p->k_batch_stride[ks], 128))
+                return -1;
+            if (make_map_3d(op, &L.tmV[s], p->v[ks], bf16, D, p->kv_rows[ks], p->batch, p->v_ld[ks],
+                            p->v_batch_stride[ks], 128))
+                return -1;
+        }
+        bdattn::SdpaDevArgs& a = L.args;
+        for (int s = 0; s < 2; ++s) {
+            const bool have_q = s < p->n_q_seg;
+            const bool have_k = s < p->n_kv_seg;
+            a.q_rows[s] = have_q ? p->q_rows[s] : 0;
+            a.o[s] = have_q ? p->o[s] : nullptr;
+            a.o_ld[s] = have_q ? p->o_ld[s] : 0;
+            a.o_bs[s] = have_q ? p->o_batch_stride[s] : 0;
+            a.kv_rows[s] = have_k ? p->kv_rows[s] : 0;
+        }
+        a.q_ctas0 = (a.q_rows[0] + 255) / 256;
+        const int q_ctas1 = (a.q_rows[1] + 255) / 256;
+        a.kv_tiles0 = (a.kv_rows[0] + 127) / 128;
+        a.kv_tiles = a.kv_tiles0 + (a.kv_rows[1] + 127) / 128;
+        a.mask_mode = p->mask_mode;
+        a.q_offset = static_cast<int>(Lk - Lq);
+        a.hd_out = hd;
+        a.key_mask = p->key_mask;
+        a.key_scale = p->key_scale;
+        a.val_scale = p->val_scale;
+        a.scale_log2 = scale * 1.4426950408889634f;
+        L.q_ctas = a.q_ctas0 + q_ctas1;
+        L.num_heads = p->num_heads;
+        L.batch = p->batch;
+        L.head_dim = hd;
+        L.bf16 = bf16;
+        if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
+        cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+        return 0;
+    }
+
+    bdattn::SdpaGeneralArgs g;
+    std::memset(&g, 0, sizeof(g));
+    for (int s = 0; s < 2; ++s) {
+        if (s < p->n_q_seg) {
+            g.q[s] = p->q[s]; g.o[s] = p->o[s]; g.q_rows[s] = p->q_rows[s];
+            g.q_ld[s] = p->q_ld[s]; g.o_ld[s] = p->o_ld[s];
+            g.q_bs[s] = p->q_batch_stride[s]; g.o_bs[s] = p->o_batch_stride[s];
+        }
+        if (s < p->n_kv_seg) {
+            g.k[s] = p->k[s]; g.v[s] = p->v[s]; g.kv_rows[s] = p->kv_rows[s];
+            g.k_ld[s] = p->k_ld[s]; g.v_ld[s] = p->v_ld[s];
+            g.k_bs[s] = p->k_batch_stride[s]; g.v_bs[s] = p->v_batch_stride[s];
+        }
+    }
+    g.mask_mode = p->mask_mode;
+    g.q_offset = static_cast<int>(Lk - Lq);
+    g.head_dim = hd;
+    g.key_mask = p->key_mask;
+    g.key_scale = p->key_scale;
+    g.val_scale = p->val_scale;
+    g.scale = scale;
+    cudaError_t e = bdattn::launch_sdpa_general(g, p->num_heads, p->batch, bf16, st);
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype, int num_heads,
+                        int head_dim, float eps, int pair_mode, bdattn_stream_t stream) {
+    const char* op = "bdattn_rmsnorm_rope";
+    if (require_sm100(op)) return -1;
+    if (jobs == nullptr || n_jobs < 1 || n_jobs > BDATTN_MAX_NORM_JOBS)
+        return fail("%s: n_jobs must be in [1, %d]", op, BDATTN_MAX_NORM_JOBS);
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: dtype must be BF16 or F16", op);
+    if (num_heads < 1 || head_dim < 2 || head_dim > 256 || head_dim % 2 != 0)
+        return fail("%s: head_dim must be even and <= 256 (got %d)", op, head_dim);
+    if (pair_mode != BDATTN_ROPE_INTERLEAVED && pair_mode != BDATTN_ROPE_HALF_SPLIT)
+        return fail("%s: unknown pair_mode %d", op, pair_mode);
+    bdattn::NormRopeArgs a;
+    std::memset(&a, 0, sizeof(a));
+    const long long D = static_cast<long long>(num_heads) * head_dim;
+    for (int i = 0; i < n_jobs; ++i) {
+        const bdattn_norm_rope_job& j = jobs[i];
+        if (j.x == nullptr || j.out == nullptr) return fail("%s: job %d: x/out is null", op, i);
+        if (j.rows < 1) return fail("%s: job %d: rows must be >= 1", op, i);
+        if (j.x_ld < D || j.out_ld < D) return fail("%s: job %d: ld smaller than num_heads*head_dim", op, i);
+        if ((j.cos == nullptr) != (j.sin == nullptr)) return fail("%s: job %d: cos and sin must both be given", op, i);
+        if (j.gain != nullptr && j.gain_dtype != BDATTN_F32 && j.gain_dtype != dtype)
+            return fail("%s: job %d: gain_dtype must be F32 or the tensor dtype", op, i);
+        if ((reinterpret_cast<uintptr_t>(j.x) & 3u) || (reinterpret_cast<uintptr_t>(j.out) & 3u) ||
+            (j.x_ld & 1) || (j.out_ld & 1))
+            return fail("%s: job %d: x/out must be 4-byte aligned with even ld", op, i);
+        bdattn::NormRopeJobDev& d = a.job[i];
+        d.x = j.x; d.out = j.out; d.rows = j.rows; d.x_ld = j.x_ld; d.out_ld = j.out_ld;
+        d.gain = j.gain; d.gain_is_f32 = j.gain_dtype == BDATTN_F32 ? 1 : 0;
+        d.cos = j.cos; d.sin = j.sin; d.rope_row0 = j.rope_row0;
+    }
+    a.n_jobs = n_jobs;
+    a.num_heads = num_heads;
+    a.head_dim = head_dim;
+    a.eps = eps;
+    a.pair_mode = pair_mode;
+    cudaError_t e = bdattn::launch_norm_rope(a, dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, void* out, int dtype,
+                                int batch, int num_heads, int head_dim, int n_tokens,
+                                long long ld, long long batch_stride, float eps,
+                                const float* sz_in, float w_in, float* sz_out,
+                                bdattn_stream_t stream) {
+    const char* op = "bdattn_linear_attn_relu_fwd";
+    if (require_sm100(op)) return -1;
+    if (q == nullptr || k == nullptr || v == nullptr || out == nullptr)
+        return fail("%s: q/k/v/out must not be null", op);
+    if (dtype != BDATTN_BF16)
+        return fail("%s: dtype must be BF16 (the state sums n_tokens products and overflows FP16)", op);
+    if (head_dim != 32)
+        return fail("%s: head_dim must be 32 (got %d), as the reference's Sana attention requires", op,
+                    head_dim);
+    if (batch < 1 || num_heads < 1 || n_tokens < 1)
+        return fail("%s: batch, num_heads and n_tokens must be >= 1", op);
+    if (n_tokens % 8 != 0) return fail("%s: n_tokens must be a multiple of 8 (got %d)", op, n_tokens);
+    if (ld < n_tokens || ld % 8 != 0 || batch_stride % 8 != 0 || !aligned16(q) || !aligned16(k) ||
+        !aligned16(v) || !aligned16(out))
+        return fail("%s: tensors must be 16-byte aligned, ld >= n_tokens, ld and batch_stride "
+                    "multiples of 8 elements", op);
+    bdattn::LinearAttnArgs a;
+    a.q = q; a.k = k; a.v = v; a.out = out;
+    a.batch = batch; a.num_heads = num_heads; a.n_tokens = n_tokens;
+    a.ld = ld; a.batch_stride = batch_stride > 0 ? batch_stride : static_cast<long long>(num_heads) * 32 * ld;
+    a.eps = eps; a.sz_in = sz_in; a.w_in = w_in; a.sz_out = sz_out;
+    const long long D = static_cast<long long>(num_heads) * 32;
+    CUtensorMap tq, tk, tv;
+    if (make_map_3d(op, &tq, q, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
+    if (make_map_3d(op, &tk, k, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
+    if (make_map_3d(op, &tv, v, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
+    // Cluster size: spread one (batch, head) over several SMs while the grid
+    // still fits the 148 SMs and every CTA keeps at least one 128-token chunk.
+    const int chunks = (n_tokens + 127) / 128;
+    int cs = 1;
+    while (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 148 && chunks >= cs * 2) cs *= 2;
+    cudaError_t e = bdattn::launch_linear_attn(a, tq, tk, tv, cs, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,341 @@
+// Sana ReLU linear attention (head_dim 32, BF16 storage, FP32 state).
+//
+// Math (src/dit/sana.cpp:470-520), per (batch, head), channel-major (32, N)
+// operands Q, K, V:
+//   [S; z] = [V; 1] relu(K)^T            (33 x 32, summed over the N tokens)
+//   out    = (S relu(Q)) / (z relu(Q) + eps)
+//
+// One thread-block cluster of CS CTAs (CS in {1, 2, 4, 8}, picked so that
+// batch * heads * CS fills the SMs) owns one (batch, head).  Each CTA streams
+// its share of the tokens twice:
+//   pass A  K and V chunks (128 tokens) -> partial [S; z] on the legacy
+//           tensor path (mma.sync m16n8k16, FP32 accumulate; the matrices are
+//           32 x 32, far below a tcgen05 tile), ReLU applied to the B
+//           fragments in registers, z summed from the same fragments;
+//   reduce  warps -> CTA in shared memory, CTA -> cluster through distributed
+//           shared memory (no global scratch);
+//   pass B  Q chunks -> out = [S; z] relu(Q) with the FP32 state split into
+//           BF16 high and low parts (two MMAs) so the state keeps ~16 bits,
+//           division by the z row, BF16 store through a staging tile.
+// Tiles arrive by TMA (64-token x 32-row boxes, 128-byte swizzle) into a ring
+// shared by both passes, so the first Q chunks are in flight during the
+// reduction.  HBM-bound: 4 * N * 32 * 2 bytes per (batch, head).
+#include <cooperative_groups.h>
+
+#include "sdpa_internal.h"
+#include "tc05.cuh"
+
+namespace bdattn {
+namespace {
+
+namespace cg = cooperative_groups;
+
+constexpr int kLaThreads = 256;
+constexpr int kLaWarps = 8;
+constexpr int kLaChunk = 128;                 // tokens per ring item
+constexpr int kLaStages = 4;
+constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
+constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
+constexpr int kLaState = 33 * 32;             // [S; z] floats
+constexpr int kLaOutLd = 136;                 // staging row stride (elements)
+
+struct LaSmem {
+    alignas(1024) uint8_t ring[kLaStages][kLaSlotBytes];
+    float partial[kLaWarps][kLaState];
+    float local_state[kLaState];
+    float state[48 * 32];   // rows 33..47 zero
+    alignas(16) __nv_bfloat16 out_stage[2][32 * kLaOutLd];
+    uint64_t full[kLaStages];
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
+                                        uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1,
+                                              uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                         uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+        "{%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t relu2(uint32_t w) {
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&w);
+    x = __hmax2(x, __float2bfloat162_rn(0.0f));
+    return *reinterpret_cast<uint32_t*>(&x);
+}
+__device__ __forceinline__ float sum2(uint32_t w) {
+    return __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
+}
+// Byte offset of (row, 16-byte chunk) inside a 128-byte-swizzled 32 x 64 box.
+__device__ __forceinline__ uint32_t swz(int row, int chunk) {
+    return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
+}
+
+__global__ void __launch_bounds__(kLaThreads)
+linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const LinearAttnArgs a) {
+    extern __shared__ uint8_t la_raw[];
+    LaSmem& sm = *reinterpret_cast<LaSmem*>((reinterpret_cast<uintptr_t>(la_raw) + 1023) &
+                                            ~static_cast<uintptr_t>(1023));
+    cg::cluster_group cluster = cg::this_cluster();
+    const int cs = static_cast<int>(cluster.num_blocks());
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int head = blockIdx.y;
+    const int batch = blockIdx.z;
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int g = lane >> 2;
+    const int q4 = lane & 3;
+
+    const int chunks = (a.n_tokens + kLaChunk - 1) / kLaChunk;
+    const int cpc = (chunks + cs - 1) / cs;
+    const int c_begin = min(rank * cpc, chunks);
+    const int c_end = min(c_begin + cpc, chunks);
+    const int n_mine = c_end - c_begin;
+    const int n_items = 2 * n_mine;   // pass A items, then pass B items
+    const int row0 = head * 32;
+
+    if (tid == 0) {
+        for (int s = 0; s < kLaStages; ++s) mbar_init(&sm.full[s], 1);
+        fence_mbar_init();
+    }
+    for (int i = tid; i < 48 * 32; i += kLaThreads) sm.state[i] = 0.0f;
+    __syncthreads();
+
+    auto issue = [&](int item) {
+        const int slot = item % kLaStages;
+        uint8_t* dst = sm.ring[slot];
+        if (item < n_mine) {
+            const int tok = (c_begin + item) * kLaChunk;
+            mbar_arrive_expect_tx(&sm.full[slot], 4 * kLaBoxBytes);
+            tma_load_3d(dst, &tmK, &sm.full[slot], tok, row0, batch);
+            tma_load_3d(dst + kLaBoxBytes, &tmK, &sm.full[slot], tok + 64, row0, batch);
+            tma_load_3d(dst + 2 * kLaBoxBytes, &tmV, &sm.full[slot], tok, row0, batch);
+            tma_load_3d(dst + 3 * kLaBoxBytes, &tmV, &sm.full[slot], tok + 64, row0, batch);
+        } else {
+            const int tok = (c_begin + item - n_mine) * kLaChunk;
+            mbar_arrive_expect_tx(&sm.full[slot], 2 * kLaBoxBytes);
+            tma_load_3d(dst, &tmQ, &sm.full[slot], tok, row0, batch);
+            tma_load_3d(dst + kLaBoxBytes, &tmQ, &sm.full[slot], tok + 64, row0, batch);
+        }
+    };
+    if (tid == 0) {
+        for (int it = 0; it < min(kLaStages, n_items); ++it) issue(it);
+    }
+
+    bool ok = true;
+    // ------------------------------------------------------------- pass A
+    float acc[2][4][4];
+    float zacc[4];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[mt][nt][i] = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) zacc[nt] = 0.0f;
+
+    const int box = warp >> 2;           // which 64-token box of the chunk
+    const int chunk0 = (warp & 3) * 2;   // first 16-byte chunk of this warp's 16 tokens
+    for (int it = 0; it < n_mine; ++it) {
+        const int slot = it % kLaStages;
+        ok = mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1));
+        if (!__all_sync(0xffffffffu, ok)) ok = false;
+        if (ok) {
+            const uint32_t kb = smem_u32(sm.ring[slot]) + box * kLaBoxBytes;
+            const uint32_t vb = kb + 2 * kLaBoxBytes;
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt) {
+                const int row = mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                ldsm_x4(vb + swz(row, chunk0 + (lane >> 4)), af[mt][0], af[mt][1], af[mt][2], af[mt][3]);
+            }
+#pragma unroll
+            for (int np = 0; np < 2; ++np) {
+                const int mi = lane >> 3;
+                const int row = np * 16 + (mi >> 1) * 8 + (lane & 7);
+                uint32_t b[4];
+                ldsm_x4(kb + swz(row, chunk0 + (mi & 1)), b[0], b[1], b[2], b[3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
+                zacc[2 * np] += sum2(b[0]) + sum2(b[1]);
+                zacc[2 * np + 1] += sum2(b[2]) + sum2(b[3]);
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    mma_bf16(acc[mt][2 * np], af[mt][0], af[mt][1], af[mt][2], af[mt][3], b[0], b[1]);
+                    mma_bf16(acc[mt][2 * np + 1], af[mt][0], af[mt][1], af[mt][2], af[mt][3], b[2], b[3]);
+                }
+            }
+        }
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;   // CTA-uniform from here on
+        if (tid == 0 && ok && it + kLaStages < n_items) issue(it + kLaStages);
+        if (!ok) break;
+    }
+
+    // ------------------------------------------------------------- reduce
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            float* p = sm.partial[warp];
+            const int i0 = mt * 16 + g;
+            const int j0 = nt * 8 + q4 * 2;
+            p[i0 * 32 + j0] = acc[mt][nt][0];
+            p[i0 * 32 + j0 + 1] = acc[mt][nt][1];
+            p[(i0 + 8) * 32 + j0] = acc[mt][nt][2];
+            p[(i0 + 8) * 32 + j0 + 1] = acc[mt][nt][3];
+        }
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        float z = zacc[nt];
+        z += __shfl_xor_sync(0xffffffffu, z, 1);
+        z += __shfl_xor_sync(0xffffffffu, z, 2);
+        if (q4 == 0) sm.partial[warp][32 * 32 + nt * 8 + g] = z;
+    }
+    __syncthreads();
+    for (int i = tid; i < kLaState; i += kLaThreads) {
+        float s = 0.0f;
+#pragma unroll
+        for (int w = 0; w < kLaWarps; ++w) s += sm.partial[w][i];
+        sm.local_state[i] = s;
+    }
+    cluster.sync();
+    for (int i = tid; i < kLaState; i += kLaThreads) {
+        float s = 0.0f;
+        for (int r = 0; r < cs; ++r) {
+            const float* remote = cluster.map_shared_rank(sm.local_state, r);
+            s += remote[i];
+        }
+        const long long so = (static_cast<long long>(batch) * a.num_heads + head) * kLaState + i;
+        if (a.sz_out != nullptr && rank == 0) a.sz_out[so] = s;
+        if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
+        sm.state[i] = s;
+    }
+    cluster.sync();
+
+    // ------------------------------------------------------------- pass B
+    // A fragments of [S; z] (48 x 32, rows 33.. zero), split hi + lo.
+    uint32_t ah[3][2][4], al[3][2][4];
+#pragma unroll
+    for (int mt = 0; mt < 3; ++mt)
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int row = mt * 16 + g + (r & 1) * 8;
+                const int col = ks * 16 + q4 * 2 + (r >> 1) * 8;
+                const float x0 = sm.state[row * 32 + col];
+                const float x1 = sm.state[row * 32 + col + 1];
+                const float h0 = __bfloat162float(__float2bfloat16_rn(x0));
+                const float h1 = __bfloat162float(__float2bfloat16_rn(x1));
+                ah[mt][ks][r] = pack2<true>(h0, h1);
+                al[mt][ks][r] = pack2<true>(x0 - h0, x1 - h1);
+            }
+
+    for (int it = n_mine; ok && it < n_items; ++it) {
+        const int slot = it % kLaStages;
+        ok = mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1));
+        if (!__all_sync(0xffffffffu, ok)) ok = false;
+        const int cidx = it - n_mine;
+        __nv_bfloat16* stage = sm.out_stage[cidx & 1];
+        if (ok) {
+            const uint32_t qb = smem_u32(sm.ring[slot]) + box * kLaBoxBytes;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                uint32_t b[4];
+                ldsm_x4_trans(qb + swz(lane, chunk0 + nt), b[0], b[1], b[2], b[3]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
+                float o[3][4];
+#pragma unroll
+                for (int mt = 0; mt < 3; ++mt) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) o[mt][i] = 0.0f;
+#pragma unroll
+                    for (int ks = 0; ks < 2; ++ks) {
+                        mma_bf16(o[mt], ah[mt][ks][0], ah[mt][ks][1], ah[mt][ks][2], ah[mt][ks][3],
+                                 b[2 * ks], b[2 * ks + 1]);
+                        mma_bf16(o[mt], al[mt][ks][0], al[mt][ks][1], al[mt][ks][2], al[mt][ks][3],
+                                 b[2 * ks], b[2 * ks + 1]);
+                    }
+                }
+                // Row 32 (z . relu(q)) sits in row 0 of the third tile: lanes 0..3.
+                const float den0 = __shfl_sync(0xffffffffu, o[2][0], q4);
+                const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
+                const float r0 = 1.0f / (den0 + a.eps);
+                const float r1 = 1.0f / (den1 + a.eps);
+                const int tok = warp * 16 + nt * 8 + q4 * 2;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    const int i0 = mt * 16 + g;
+                    *reinterpret_cast<uint32_t*>(&stage[i0 * kLaOutLd + tok]) =
+                        pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
+                    *reinterpret_cast<uint32_t*>(&stage[(i0 + 8) * kLaOutLd + tok]) =
+                        pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
+                }
+            }
+        }
+        ok = __syncthreads_and(ok ? 1 : 0) != 0;
+        if (tid == 0 && ok && it + kLaStages < n_items) issue(it + kLaStages);
+        if (ok) {
+            const int tok0 = (c_begin + cidx) * kLaChunk;
+#pragma unroll
+            for (int rep = 0; rep < 2; ++rep) {
+                const int idx = tid + rep * kLaThreads;
+                const int row = idx >> 4;
+                const int c16 = idx & 15;
+                const int tok = tok0 + c16 * 8;
+                if (tok < a.n_tokens) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(&stage[row * kLaOutLd + c16 * 8]);
+                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) +
+                                         static_cast<long long>(batch) * a.batch_stride +
+                                         static_cast<long long>(row0 + row) * a.ld + tok;
+                    *reinterpret_cast<uint4*>(dst) = w;
+                }
+            }
+        }
+    }
+    if (!ok && tid == 0) {
+        // Unwinding after a wait ran out: let copies in flight land.
+        for (int s = 0; s < kLaStages; ++s) mbar_wait(&sm.full[s], 0);
+    }
+    cluster.sync();
+}
+
+}  // namespace
+
+cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
+                               const CUtensorMap& tmV, int cluster_size, cudaStream_t stream) {
+    const size_t smem = sizeof(LaSmem) + 1024;
+    cudaError_t e = cudaFuncSetAttribute(linear_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(smem));
+    if (e != cudaSuccess) return e;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(cluster_size), static_cast<unsigned>(a.num_heads),
+                       static_cast<unsigned>(a.batch));
+    cfg.blockDim = dim3(kLaThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_size);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, linear_attn_kernel, tmQ, tmK, tmV, a);
+}
+
+}  // namespace bdattn

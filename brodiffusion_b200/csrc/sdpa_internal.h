@@ -1,0 +1,100 @@
+// Internal launch interfaces shared by the C-ABI layer and the kernels.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+namespace bdattn {
+
+// Device-side arguments of the softmax-attention kernels.
+struct SdpaDevArgs {
+    int q_rows[2];
+    int kv_rows[2];
+    void* o[2];
+    long long o_ld[2];
+    long long o_bs[2];
+    int q_ctas0;    // CTAs covering query segment 0
+    int kv_tiles0;  // 128-key tiles covering key segment 0
+    int kv_tiles;   // key tiles in total
+    int mask_mode;
+    int q_offset;   // Lk - Lq
+    int hd_out;     // columns stored per head
+    const float* key_mask;
+    const float* key_scale;
+    const float* val_scale;
+    float scale_log2;  // softmax scale * log2(e)
+};
+
+struct SdpaLaunch {
+    CUtensorMap tmQ[2], tmK[2], tmV[2];
+    SdpaDevArgs args;
+    int q_ctas;
+    int num_heads;
+    int batch;
+    int head_dim;
+    bool bf16;
+};
+
+cudaError_t launch_sdpa_tc05(const SdpaLaunch& L, cudaStream_t stream);
+
+// General kernel (any head_dim that is a multiple of 8 up to 256).
+struct SdpaGeneralArgs {
+    const void* q[2];
+    const void* k[2];
+    const void* v[2];
+    void* o[2];
+    int q_rows[2];
+    int kv_rows[2];
+    long long q_ld[2], k_ld[2], v_ld[2], o_ld[2];
+    long long q_bs[2], k_bs[2], v_bs[2], o_bs[2];
+    int mask_mode;
+    int q_offset;
+    int head_dim;
+    const float* key_mask;
+    const float* key_scale;
+    const float* val_scale;
+    float scale;
+};
+cudaError_t launch_sdpa_general(const SdpaGeneralArgs& a, int num_heads, int batch, bool bf16,
+                                cudaStream_t stream);
+
+// Per-head RMSNorm + RoPE.
+struct NormRopeJobDev {
+    const void* x;
+    void* out;
+    int rows;
+    long long x_ld;
+    long long out_ld;
+    const void* gain;
+    int gain_is_f32;
+    const float* cos;
+    const float* sin;
+    int rope_row0;
+};
+struct NormRopeArgs {
+    NormRopeJobDev job[4];
+    int n_jobs;
+    int num_heads;
+    int head_dim;
+    float eps;
+    int pair_mode;
+};
+cudaError_t launch_norm_rope(const NormRopeArgs& a, bool bf16, cudaStream_t stream);
+
+// Sana ReLU linear attention.
+struct LinearAttnArgs {
+    const void* q;
+    const void* k;
+    const void* v;
+    void* out;
+    int batch, num_heads, n_tokens;
+    long long ld, batch_stride;
+    float eps;
+    const float* sz_in;
+    float w_in;
+    float* sz_out;
+};
+cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
+                               const CUtensorMap& tmV, int cluster_size, cudaStream_t stream);
+
+}  // namespace bdattn

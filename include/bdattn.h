@@ -1,0 +1,182 @@
+/* bdattn — C ABI of the B200 (sm_100a) denoiser-attention library.
+ *
+ * This is the boundary a brodiffusion build binds instead of the brotensor
+ * attention operators and its own fused_transformer entry points.  Every
+ * declaration cites the reference interface it replaces (path within the
+ * brodiffusion source tree : line).
+ *
+ * Conventions (taken from the reference's own C ABI,
+ * include/brodiffusion/qwenimage21_capi.h:32-37):
+ *   - every function returns 0 on success and -1 on failure;
+ *     bdattn_last_error() returns the calling thread's last message;
+ *   - all tensor pointers are caller-owned DEVICE pointers on the current CUDA
+ *     device; tensors are dense row-major 2-D (rows, cols) with an explicit
+ *     row stride `ld` in elements; heads are column blocks (head h of an
+ *     (L, nh*hd) tensor is columns [h*hd, (h+1)*hd));
+ *   - work is enqueued on the given stream and the call returns without
+ *     synchronising (include/brodiffusion/unet.h:50-51); no function
+ *     allocates device memory: an operator that needs scratch takes it as an
+ *     argument, with a bdattn_*_workspace_bytes() query beside it;
+ *   - there is no CPU path: a call fails if no sm_100 device is current.
+ */
+#ifndef BDATTN_H_
+#define BDATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* bdattn_stream_t; /* == cudaStream_t */
+
+/* Element types; values follow brotensor::Dtype order as used by the callers
+ * (FP32, FP16, BF16). */
+enum { BDATTN_F32 = 0, BDATTN_F16 = 1, BDATTN_BF16 = 2 };
+
+/* Attention visibility rules. */
+enum {
+    BDATTN_MASK_NONE = 0,
+    /* key j visible to query i iff j <= i + (Lk - Lq): what
+     * flash_attention_windowed_forward(window = 0) and causal = true compute
+     * (src/dit/qwenimage21_forward.cpp:659-662). */
+    BDATTN_MASK_CAUSAL = 1
+};
+
+/* Rotary pair conventions for bdattn_rmsnorm_rope. */
+enum {
+    BDATTN_ROPE_INTERLEAVED = 0, /* pair p = head elements (2p, 2p+1) */
+    BDATTN_ROPE_HALF_SPLIT = 1   /* pair p = head elements (p, p + hd/2) */
+};
+
+/* Bits of the per-device status word (bdattn_device_status). */
+enum { BDATTN_STATUS_WAIT_TIMEOUT = 1, BDATTN_STATUS_BAD_ARGS = 2 };
+
+/* Library version (major*10000 + minor*100 + patch). */
+int bdattn_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* bdattn_last_error(void);
+
+/* Synchronises the current device and returns its status word: 0 when every
+ * kernel ran to completion; a bit of BDATTN_STATUS_* when a kernel gave up a
+ * bounded wait or rejected its arguments.  clear != 0 resets the word.
+ * Replaces BRODIFFUSION_CUDA_CHECK(cudaGetLastError())
+ * (include/brodiffusion/detail/cuda_check.cuh:13-21) for device-side
+ * failures that do not fault. */
+int bdattn_device_status(int* status, int clear);
+
+/* ---------------------------------------------------------------- softmax
+ * Multi-head softmax attention  O = softmax(Q K^T * scale [masks]) V.
+ *
+ * Replaces brotensor::flash_attention_forward (call sites
+ * src/dit/common.cpp:194, src/dit/qwenimage21_forward.cpp:648,667,674,
+ * src/dit/sana.cpp:623) and brotensor::flash_attention_windowed_forward
+ * (src/dit/qwenimage21_forward.cpp:662).
+ *
+ * Queries/outputs and keys/values may each be given as ONE or TWO row
+ * segments that are attended as if concatenated (segment 0 first).  That
+ * removes the concat_rows/slice_rows copies of the Flux double-stream block
+ * (src/dit/flux.cpp:491-494,514-516: text rows, then image rows) and the
+ * k_full_/v_full_ copies of the Qwen-Image cached step
+ * (src/dit/qwenimage21_forward.cpp:600-647: cached prefix rows, then fresh
+ * rows).  `o_ld` lets the output land inside a wider row (the Flux
+ * single-stream cat5_ buffer, src/dit/flux.cpp:626-632).
+ *
+ * key_scale / val_scale (optional, Lk floats each over the concatenated keys)
+ * multiply K rows and V rows on the fly: the prefix K/V attenuation hook of
+ * src/dit/qwenimage21_forward.cpp:606-645 without touching the cache.
+ *
+ * head_dim 64 and 128 run on the tcgen05 tensor-core kernel; other head
+ * dims (multiple of 8, <= 256) run on a general kernel.  dtype BF16 or F16.
+ */
+typedef struct bdattn_sdpa_params {
+    int dtype;
+    int batch;
+    int num_heads;
+    int head_dim;
+    int n_q_seg;                 /* 1 or 2 */
+    const void* q[2];
+    void* o[2];
+    int q_rows[2];
+    long long q_ld[2];
+    long long o_ld[2];
+    long long q_batch_stride[2]; /* elements between batch items */
+    long long o_batch_stride[2];
+    int n_kv_seg;                /* 1 or 2 */
+    const void* k[2];
+    const void* v[2];
+    int kv_rows[2];
+    long long k_ld[2];
+    long long v_ld[2];
+    long long k_batch_stride[2];
+    long long v_batch_stride[2];
+    int mask_mode;               /* BDATTN_MASK_* */
+    const float* key_mask;       /* Lk floats, 1 = valid, 0 = masked; or NULL */
+    const float* key_scale;      /* Lk floats or NULL */
+    const float* val_scale;      /* Lk floats or NULL */
+    float softmax_scale;         /* 0 => 1/sqrt(head_dim) */
+} bdattn_sdpa_params;
+
+int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
+
+/* ------------------------------------------------- per-head RMSNorm + RoPE
+ * out = rope(rms_norm_heads(x) * gain).  Replaces the headnorm view +
+ * brotensor::rms_norm_forward (src/dit/flux.cpp:462-469,
+ * src/dit/qwenimage21_forward.cpp:54-63) followed by brotensor::rope_apply
+ * (src/dit/common.cpp:192-193, src/dit/qwenimage21_forward.cpp:584-585) in
+ * one pass over the tensor.
+ *   x, out : (rows, num_heads*head_dim), dtype BF16/F16, may alias;
+ *   gain   : head_dim values of gain_dtype (F32, or the tensor dtype), or
+ *            NULL to skip the norm;
+ *   cos, sin : FP32 (table_rows, head_dim/2) tables, or both NULL to skip
+ *            the rotation; row r of x uses table row (rope_row0 + r).
+ * Up to BDATTN_MAX_NORM_JOBS independent jobs run in one launch (the four
+ * norms of a Flux double-stream block).
+ */
+#define BDATTN_MAX_NORM_JOBS 4
+typedef struct bdattn_norm_rope_job {
+    const void* x;
+    void* out;
+    int rows;
+    long long x_ld;
+    long long out_ld;
+    const void* gain;
+    int gain_dtype;
+    const float* cos;
+    const float* sin;
+    int rope_row0;
+} bdattn_norm_rope_job;
+
+int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype, int num_heads,
+                        int head_dim, float eps, int pair_mode, bdattn_stream_t stream);
+
+/* ------------------------------------------------ ReLU linear attention
+ * Sana self-attention core.  Replaces the op sequence of
+ * SanaDenoiser::self_attention_ (src/dit/sana.cpp:521-586; FP32 statement of
+ * the same math at 470-520):
+ *   per head h:  [S; z] = [V_h; 1] relu(K_h)^T,
+ *                out_h  = (S relu(Q_h)) / (z relu(Q_h) + eps).
+ *   q, k, v, out : channel-major (num_heads*head_dim, n_tokens), row stride
+ *                  ld, `batch` items batch_stride apart; head_dim == 32
+ *                  (src/dit/sana.cpp:176-178);
+ *   sz_in  : optional FP32 (batch, num_heads, head_dim+1, head_dim) state
+ *            added with weight w_in before the query read (inject seam,
+ *            src/dit/sana.cpp:550-559);
+ *   sz_out : optional FP32 state output taken before injection (capture
+ *            seam).
+ * One thread-block cluster per (batch, head) reduces the state through
+ * distributed shared memory, so the operator needs no scratch memory.
+ */
+int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, void* out, int dtype,
+                                int batch, int num_heads, int head_dim, int n_tokens,
+                                long long ld, long long batch_stride, float eps,
+                                const float* sz_in, float w_in, float* sz_out,
+                                bdattn_stream_t stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* BDATTN_H_ */
