@@ -1,0 +1,398 @@
+#!/usr/bin/env python
+"""Benchmark of the denoiser-attention hot path.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--workload flux1024|flux2048_headsharded]
+
+One step = one pass of the hot path over one synthetic batch:
+  flux1024              (1 GPU)  Flux.1 joint attention at 1024 px, double-stream
+                        form: per-head QK RMSNorm + 3-axis RoPE (one launch, four
+                        jobs) and the joint softmax attention of 512 text + 4096
+                        image tokens, 24 heads x 128 (one launch).
+  flux2048_headsharded  (N GPUs) Flux.1 joint attention at 2048 px, batch 2,
+                        512 + 16384 tokens; heads split over the ranks, NCCL
+                        all-gather of the per-head outputs.  Default for N > 1.
+The metric is attention TFLOP/s with the reference's own FLOP convention
+(4 * Lq * Lk * heads * head_dim, tools/bench_krea2_kernels.cpp:188-192).
+
+Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement
+of the reference path (oracle/) on the host cores instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+NH, HD = 24, 128
+D = NH * HD
+WORKLOADS = {
+    # name: (batch, text rows, latent rows, latent cols)
+    "flux1024": (1, 512, 64, 64),
+    "flux2048_headsharded": (2, 512, 128, 128),
+}
+# dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_tc05_kernel launch
+# on the flux1024 workload, from the ncu capture summarised under profiles/.
+NCU_TRAFFIC_BYTES = {"flux1024": None}
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._period = period_s
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            self._stop.wait(self._period)
+
+    def start(self):
+        if self._nv is not None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def attention_flops(batch, L):
+    return 4.0 * batch * L * L * D
+
+
+# ----------------------------------------------------------------- reference
+def run_reference(args, rank, world):
+    """CPU restatement of the reference path on the host cores (all threads)."""
+    if rank != 0:
+        return
+    import numpy as np
+    import synth
+    from oracle import oracle as O
+    O.build()
+    batch, txt, hp, wp = WORKLOADS[args.workload]
+    L = txt + hp * wp
+    cores = O.hardware_threads()
+    q = synth.activations((L, D), 11)
+    k = synth.activations((L, D), 12)
+    v = synth.activations((L, D), 13)
+    # size one step to a bounded sample: aim for ~120 s in total
+    probe_rows = np.arange(0, L, L // 16, dtype=np.int32)[:16]
+    t0 = time.perf_counter()
+    O.sdpa(q, k, v, NH, rows=probe_rows, precise=False)
+    per_row = (time.perf_counter() - t0) / len(probe_rows)
+    n_steps = args.steps + args.warmup
+    rows_n = int(max(16, min(L, (120.0 / n_steps) / per_row)))
+    rows = np.linspace(0, L - 1, rows_n).astype(np.int32)
+    for _ in range(args.warmup):
+        O.sdpa(q, k, v, NH, rows=rows, precise=False)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.sdpa(q, k, v, NH, rows=rows, precise=False)
+    dt = (time.perf_counter() - t0) / args.steps
+    tflops = 4.0 * rows_n * L * D / dt / 1e12
+    sample = (f"{rows_n} of {L} query rows per step (all {NH} heads, all {L} keys), attention "
+              f"core in FP32, batch item 0; full-call time extrapolates to "
+              f"{batch * L / rows_n * dt * 1e3:.0f} ms")
+    line = {
+        "impl": "reference", "metric": "attention TFLOP/s", "value": tflops, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": batch * L / rows_n * dt * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "batch": batch, "tokens": L, "heads": NH,
+                   "head_dim": HD},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------- ours
+def run_ours(args, rank, world, local_rank):
+    import numpy as np
+    import torch
+    import synth
+    import brodiffusion_b200 as bd
+    from brodiffusion_b200 import headshard
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    batch, txt, hp, wp = WORKLOADS[args.workload]
+    L = txt + hp * wp
+    h0, h1 = headshard.head_range(NH, world, rank)
+    nh_l = h1 - h0
+    d_l = nh_l * HD
+    flops = attention_flops(batch, L)
+
+    cos, sin = bd.rope_tables_flux(txt, hp, wp, HD, device=dev)
+    gains = [torch.from_numpy(synth.gains(HD, 20 + i)).to(dev).bfloat16() for i in range(4)]
+
+    # Rotating input sets so that consecutive steps do not find their inputs in L2.
+    set_bytes = 3 * batch * L * d_l * 2
+    n_sets = max(2, int(np.ceil(160e6 / set_bytes)) + 1)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    sets = []
+    for _ in range(n_sets):
+        sets.append(tuple(torch.randn(batch, L, d_l, device=dev, dtype=torch.bfloat16, generator=gen)
+                          for _ in range(3)))
+    qr = torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16)
+    kr = torch.empty_like(qr)
+    staging = torch.empty(headshard.staging_shape(world, batch, L, NH, HD), device=dev,
+                          dtype=torch.bfloat16)
+    out = staging[rank]
+
+    def norm_rope(q, k):
+        for b in range(batch):
+            bd.rmsnorm_rope([
+                dict(x=q[b, :txt], out=qr[b, :txt], gain=gains[2], cos=cos, sin=sin, rope_row0=0),
+                dict(x=q[b, txt:], out=qr[b, txt:], gain=gains[0], cos=cos, sin=sin, rope_row0=txt),
+                dict(x=k[b, :txt], out=kr[b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
+                dict(x=k[b, txt:], out=kr[b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
+            ], nh_l, HD)
+
+    def attention(v):
+        bd.sdpa_fwd([qr[:, :txt], qr[:, txt:]], [kr[:, :txt], kr[:, txt:]], [v[:, :txt], v[:, txt:]],
+                    [out[:, :txt], out[:, txt:]], nh_l)
+
+    launches_per_step = batch + 1
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        norm_rope(q, k)
+        attention(v)
+        if world > 1:
+            headshard.all_gather_heads(staging)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    if bd.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during warm-up")
+
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    sampler.start()
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    if len(sampler.samples) < 5:
+        # the timed region was shorter than a few sampling periods: keep
+        # sampling over ~0.5 s of the same steps (untimed)
+        t_end = time.perf_counter() + 0.5
+        i = 0
+        while time.perf_counter() < t_end:
+            step(i)
+            i += 1
+            if i % 8 == 0:
+                torch.cuda.synchronize()
+        torch.cuda.synchronize()
+    sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if bd.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during the timed region")
+
+    # dominant kernel alone, for the roofline (events on the launching stream)
+    q, k, v = sets[0]
+    norm_rope(q, k)
+    torch.cuda.synchronize()
+    k_iters = max(5, min(50, args.steps))
+    ke = [torch.cuda.Event(enable_timing=True) for _ in range(2 * k_iters)]
+    for i in range(k_iters):
+        _, _, v = sets[i % n_sets]
+        ke[2 * i].record()
+        attention(v)
+        ke[2 * i + 1].record()
+    torch.cuda.synchronize()
+    kernel_ms = sum(ke[2 * i].elapsed_time(ke[2 * i + 1]) for i in range(k_iters)) / k_iters
+    peak_tf, peak_gbs, peak_kind = measured_peaks()
+    local_flops = flops * nh_l / NH
+    achieved = local_flops / (kernel_ms * 1e-3) / 1e12
+
+    # end to end: host buffers in, result back to the host, every step
+    hq, hk, hv = (torch.randn(batch, L, d_l, dtype=torch.bfloat16).pin_memory() for _ in range(3))
+    ho = torch.empty(batch, L, d_l, dtype=torch.bfloat16).pin_memory()
+    dq, dk, dv = (torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16) for _ in range(3))
+
+    def e2e_step():
+        dq.copy_(hq, non_blocking=True)
+        dk.copy_(hk, non_blocking=True)
+        dv.copy_(hv, non_blocking=True)
+        norm_rope(dq, dk)
+        attention(dv)
+        if world > 1:
+            headshard.all_gather_heads(staging)
+        ho.copy_(out, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+
+    line = None
+    if rank == 0:
+        clocks = sampler.summary()
+        line = {
+            "metric": "attention TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": batch, "tokens": L, "text_tokens": txt,
+                       "heads": NH, "head_dim": HD, "heads_per_gpu": nh_l,
+                       "step": "rmsnorm+rope (Q,K) -> joint softmax attention" +
+                               (" -> NCCL all-gather of head outputs" if world > 1 else ""),
+                       "l2": f"rotating {n_sets} input sets ({n_sets * set_bytes / 1e6:.0f} MB > 126 MB L2)"},
+            "clocks": clocks,
+            "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 3 * batch * L * d_l * 2,
+                    "d2h_bytes_per_step": batch * L * d_l * 2},
+            "gpu_launches": launches_per_step * args.steps,
+            "roofline": {"bound": "tensor", "kernel": "sdpa_tc05_kernel", "achieved": achieved,
+                         "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
+                         "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "kernel_ms": kernel_ms,
+                         "frac_of_nominal_2250": achieved / 2250.0,
+                         "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(L)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def cpu_baseline(L):
+    """Oracle port of the reference attention core on the host cores, on a
+    bounded sample of the same workload (about 10-20 s of CPU work)."""
+    import numpy as np
+    import synth
+    from oracle import oracle as O
+    O.build()
+    cores = O.hardware_threads()
+    q = synth.activations((L, D), 11)
+    k = synth.activations((L, D), 12)
+    v = synth.activations((L, D), 13)
+    probe = np.arange(0, L, L // 16, dtype=np.int32)[:16]
+    t0 = time.perf_counter()
+    O.sdpa(q, k, v, NH, rows=probe, precise=False)
+    per_row = (time.perf_counter() - t0) / len(probe)
+    rows_n = int(max(16, min(L, 12.0 / per_row)))
+    rows = np.linspace(0, L - 1, rows_n).astype(np.int32)
+    t0 = time.perf_counter()
+    O.sdpa(q, k, v, NH, rows=rows, precise=False)
+    dt = time.perf_counter() - t0
+    return {"value": 4.0 * rows_n * L * D / dt / 1e12, "unit": "TFLOP/s", "cores": cores,
+            "kind": "port",
+            "sample": f"{rows_n} of {L} query rows (all {NH} heads, all keys), attention core "
+                      f"FP32, {dt:.1f} s; full call extrapolates to {L / rows_n * dt:.1f} s"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.workload is None:
+        args.workload = "flux1024" if max(world, args.gpus) == 1 else "flux2048_headsharded"
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with "
+                         "python -m torch.distributed.run --nproc-per-node N bench.py --gpus N")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

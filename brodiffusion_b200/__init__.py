@@ -19,7 +19,7 @@ from . import _build
 __all__ = [
     "BdattnError", "lib", "lib_path", "F32", "F16", "BF16", "MASK_NONE", "MASK_CAUSAL",
     "ROPE_INTERLEAVED", "ROPE_HALF_SPLIT", "SdpaParams", "NormRopeJob", "sdpa_fwd",
-    "rmsnorm_rope", "linear_attn_relu_fwd", "device_status", "last_error",
+    "rmsnorm_rope", "linear_attn_relu_fwd", "rope_tables_flux", "rope_tables_qwen", "RopeSegment", "device_status", "last_error",
 ]
 
 F32, F16, BF16 = 0, 1, 2
@@ -59,6 +59,11 @@ class NormRopeJob(C.Structure):
     ]
 
 
+class RopeSegment(C.Structure):
+    """Mirror of ``bdattn_rope_segment`` (include/bdattn.h)."""
+    _fields_ = [("kind", C.c_int), ("n_tokens", C.c_int), ("h", C.c_int), ("w", C.c_int)]
+
+
 _lib = None
 
 
@@ -86,6 +91,13 @@ def lib():
             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
             C.c_int, C.c_longlong, C.c_longlong, C.c_float, C.c_void_p, C.c_float, C.c_void_p,
             C.c_void_p]
+        L.bdattn_rope_tables_flux.argtypes = [C.c_int, C.c_int, C.c_int, C.c_int,
+                                              C.POINTER(C.c_int), C.c_int, C.c_float,
+                                              C.c_void_p, C.c_void_p, C.c_void_p]
+        L.bdattn_rope_rows_qwen.argtypes = [C.POINTER(RopeSegment), C.c_int, C.c_int, C.c_int]
+        L.bdattn_rope_tables_qwen.argtypes = [C.POINTER(RopeSegment), C.c_int, C.c_int, C.c_int,
+                                              C.c_int, C.POINTER(C.c_int), C.c_float,
+                                              C.c_void_p, C.c_void_p, C.c_void_p]
         _lib = L
     return _lib
 
@@ -198,6 +210,40 @@ def rmsnorm_rope(jobs, num_heads, head_dim, *, eps=1e-6, pair_mode=ROPE_INTERLEA
         arr[i].rope_row0 = j.get("rope_row0", 0)
     _check(lib().bdattn_rmsnorm_rope(arr, len(jobs), dtype, num_heads, head_dim, eps, pair_mode,
                                      _stream(stream)))
+
+
+def rope_tables_flux(txt_len, hp, wp, head_dim, axes=(16, 56, 56), theta=10000.0, *,
+                     device=None, stream=None):
+    """``bdattn_rope_tables_flux`` -> (cos, sin) FP32 CUDA tensors (L, head_dim/2)."""
+    import torch
+    L = txt_len + hp * wp
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    cos = torch.empty(max(L, 1), head_dim // 2, device=device, dtype=torch.float32)
+    sin = torch.empty_like(cos)
+    ax = (C.c_int * len(axes))(*axes)
+    _check(lib().bdattn_rope_tables_flux(txt_len, hp, wp, head_dim, ax, len(axes), theta,
+                                         cos.data_ptr(), sin.data_ptr(), _stream(stream)))
+    return cos, sin
+
+
+def rope_tables_qwen(prefix, hp, wp, head_dim, axes=(16, 56, 56), theta=10000.0, *,
+                     device=None, stream=None):
+    """``bdattn_rope_tables_qwen``.  prefix: list of ("text", n) / ("image", h, w)."""
+    import torch
+    segs = (RopeSegment * max(len(prefix), 1))()
+    for i, s in enumerate(prefix):
+        if s[0] == "text":
+            segs[i].kind, segs[i].n_tokens = 0, s[1]
+        else:
+            segs[i].kind, segs[i].h, segs[i].w = 1, s[1], s[2]
+    rows = lib().bdattn_rope_rows_qwen(segs, len(prefix), hp, wp)
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    cos = torch.empty(max(rows, 1), head_dim // 2, device=device, dtype=torch.float32)
+    sin = torch.empty_like(cos)
+    ax = (C.c_int * 3)(*axes)
+    _check(lib().bdattn_rope_tables_qwen(segs, len(prefix), hp, wp, head_dim, ax, theta,
+                                         cos.data_ptr(), sin.data_ptr(), _stream(stream)))
+    return cos, sin
 
 
 def linear_attn_relu_fwd(q, k, v, out, num_heads, head_dim, *, eps=1e-15, sz_in=None, w_in=0.0,

@@ -5,4 +5,5 @@
 #include "sdpa_general.cu"
 #include "norm_rope.cu"
 #include "linear_attn.cu"
+#include "rope_tables.cu"
 #include "capi.cu"

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "sdpa_internal.h"
@@ -89,6 +90,17 @@ int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
                     batch, ld, batch_stride);
     }
     return 0;
+}
+
+// Share of the softmax exponentials evaluated on the FMA pipe (of every 8).
+// BDATTN_SDPA_EMU overrides the default for tuning runs.
+int sdpa_emu_setting() {
+    static int v = [] {
+        const char* e = std::getenv("BDATTN_SDPA_EMU");
+        int x = e ? std::atoi(e) : 0;
+        return (x == 0 || x == 2 || x == 4 || x == 6) ? x : 0;
+    }();
+    return v;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -202,6 +214,7 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
         L.batch = p->batch;
         L.head_dim = hd;
         L.bf16 = bf16;
+        L.emu = sdpa_emu_setting();
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
         cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
@@ -270,6 +283,90 @@ int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype,
     a.eps = eps;
     a.pair_mode = pair_mode;
     cudaError_t e = bdattn::launch_norm_rope(a, dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_rope_tables_flux(int txt_len, int hp, int wp, int head_dim, const int* axes_dims,
+                            int n_axes, float theta, float* cos, float* sin,
+                            bdattn_stream_t stream) {
+    const char* op = "build_axial_rope_tables";
+    if (require_sm100(op)) return -1;
+    if (head_dim < 2 || head_dim % 2 != 0) return fail("%s: head_dim must be even", op);
+    if (axes_dims == nullptr || n_axes < 1 || n_axes > 3) return fail("%s: n_axes must be 1..3", op);
+    int sum = 0;
+    for (int i = 0; i < n_axes; ++i) {
+        if (axes_dims[i] < 0 || axes_dims[i] % 2 != 0) return fail("%s: axes_dims_rope entries must be even", op);
+        sum += axes_dims[i];
+    }
+    if (sum != head_dim) return fail("%s: axes_dims_rope must sum to head_dim", op);
+    if (txt_len < 0 || hp < 0 || wp < 0 || txt_len + static_cast<long long>(hp) * wp < 1)
+        return fail("%s: empty sequence", op);
+    if (cos == nullptr || sin == nullptr) return fail("%s: cos/sin must not be null", op);
+    bdattn::RopeTableArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.flux = 1;
+    a.rows = txt_len + hp * wp;
+    a.half = head_dim / 2;
+    a.n_axes = n_axes;
+    for (int i = 0; i < n_axes; ++i) a.axes[i] = axes_dims[i];
+    a.theta = theta;
+    a.n_seg = 2;
+    a.seg_kind[0] = 0; a.seg_row0[0] = 0;
+    a.seg_kind[1] = 1; a.seg_row0[1] = txt_len; a.seg_h[1] = hp; a.seg_w[1] = wp > 0 ? wp : 1;
+    a.cos_out = cos; a.sin_out = sin;
+    cudaError_t e = bdattn::launch_rope_tables(a, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_rope_rows_qwen(const bdattn_rope_segment* prefix, int n_prefix, int hp, int wp) {
+    long long rows = static_cast<long long>(hp) * wp;
+    for (int i = 0; i < n_prefix; ++i)
+        rows += prefix[i].kind == 0 ? prefix[i].n_tokens : static_cast<long long>(prefix[i].h) * prefix[i].w;
+    return static_cast<int>(rows);
+}
+
+int bdattn_rope_tables_qwen(const bdattn_rope_segment* prefix, int n_prefix, int hp, int wp,
+                            int head_dim, const int* axes_dims3, float theta, float* cos,
+                            float* sin, bdattn_stream_t stream) {
+    const char* op = "build_rope_tables";
+    if (require_sm100(op)) return -1;
+    if (n_prefix < 0 || (n_prefix > 0 && prefix == nullptr)) return fail("%s: bad prefix", op);
+    if (n_prefix + 1 > bdattn::kMaxRopeSegments)
+        return fail("%s: at most %d prefix segments", op, bdattn::kMaxRopeSegments - 1);
+    if (head_dim < 2 || head_dim % 2 != 0 || axes_dims3 == nullptr) return fail("%s: head_dim must be even", op);
+    if (axes_dims3[0] + axes_dims3[1] + axes_dims3[2] != head_dim)
+        return fail("%s: axes_dims_rope must sum to head_dim", op);
+    if (hp < 1 || wp < 1) return fail("%s: target grid must be at least 1x1", op);
+    if (cos == nullptr || sin == nullptr) return fail("%s: cos/sin must not be null", op);
+    bdattn::RopeTableArgs a;
+    std::memset(&a, 0, sizeof(a));
+    a.flux = 0;
+    a.half = head_dim / 2;
+    a.n_axes = 3;
+    for (int i = 0; i < 3; ++i) a.axes[i] = axes_dims3[i];
+    a.theta = theta;
+    int row = 0, pos = 0;
+    for (int i = 0; i <= n_prefix; ++i) {
+        const bool target = i == n_prefix;
+        const int kind = target ? 1 : prefix[i].kind;
+        const int h = target ? hp : prefix[i].h;
+        const int w = target ? wp : prefix[i].w;
+        a.seg_kind[i] = kind; a.seg_row0[i] = row; a.seg_pos0[i] = pos;
+        if (kind == 0) {
+            if (prefix[i].n_tokens < 0) return fail("%s: negative segment length", op);
+            row += prefix[i].n_tokens; pos += prefix[i].n_tokens;
+        } else {
+            if (h < 1 || w < 1) return fail("%s: image segment %d must be at least 1x1", op, i);
+            a.seg_h[i] = h; a.seg_w[i] = w;
+            row += h * w; pos += (h > w ? h : w);
+        }
+    }
+    a.n_seg = n_prefix + 1;
+    a.rows = row;
+    a.cos_out = cos; a.sin_out = sin;
+    cudaError_t e = bdattn::launch_rope_tables(a, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }

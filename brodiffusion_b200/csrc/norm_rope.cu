@@ -1,8 +1,12 @@
 // Per-head RMSNorm followed by the rotary embedding, one pass over the tensor.
 //
-// One warp owns one (token, head) row of head_dim elements.  Lane l handles
-// rotary pairs l, l+32, ...; with the interleaved convention a pair is one
-// aligned 32-bit word, so a warp reads and writes whole 128-byte lines.
+// Fast path (interleaved pairs, head_dim in {8, 16, 32, 64, 128, 256}, 16-byte
+// aligned rows): every lane owns 8 consecutive elements (one 16-byte vector,
+// four rotary pairs) of one (token, head) row, head_dim/8 neighbouring lanes
+// share a row and reduce its sum of squares by shuffles, and each warp keeps
+// four such vectors in flight so that enough bytes are outstanding to fill
+// HBM.  General path: one warp per (token, head) row, lane l handles rotary
+// pairs l, l+32, ...
 // The sum of squares is accumulated in FP32 (src/dit/qwenimage21.cpp:335-337)
 // and the result is rounded to the storage type once, after the rotation.
 // Up to four independent jobs (tensor, gain, table offset) share one launch:
@@ -118,6 +122,113 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_rope_kernel(const NormRo
     }
 }
 
+
+// ---------------------------------------------------------------- fast path
+template <bool kBf16, int kLpu>   // kLpu = lanes per (token, head) row = head_dim / 8
+__global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a) {
+    constexpr int kUnroll = 4;
+    const NormRopeJobDev& job = a.job[blockIdx.y];
+    const int lane = threadIdx.x & 31;
+    const int l = lane % kLpu;                 // this lane's 8-element slot inside the head
+    const int sub = lane / kLpu;               // which row of the warp's group
+    constexpr int kUnitsPerWarp = 32 / kLpu;
+    const int hd = kLpu * 8;
+    const int half = hd / 2;
+    const long long n_units = static_cast<long long>(job.rows) * a.num_heads;
+    const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const long long n_warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+
+    float g[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) g[i] = 1.0f;
+    if (job.gain != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            g[i] = job.gain_is_f32 ? reinterpret_cast<const float*>(job.gain)[l * 8 + i]
+                                   : load1<kBf16>(job.gain, l * 8 + i);
+        }
+    }
+    const uint16_t* xin = reinterpret_cast<const uint16_t*>(job.x);
+    uint16_t* xout = reinterpret_cast<uint16_t*>(job.out);
+
+    for (long long base = warp_id * kUnroll * kUnitsPerWarp; base < n_units;
+         base += n_warps * kUnroll * kUnitsPerWarp) {
+        uint4 v[kUnroll];
+        float4 cs[kUnroll], sn[kUnroll];
+        long long ooff[kUnroll];
+        bool live[kUnroll];
+#pragma unroll
+        for (int it = 0; it < kUnroll; ++it) {
+            const long long u = base + it * kUnitsPerWarp + sub;
+            live[it] = u < n_units;
+            const long long uu = live[it] ? u : 0;
+            const int row = static_cast<int>(uu / a.num_heads);
+            const int head = static_cast<int>(uu - static_cast<long long>(row) * a.num_heads);
+            const long long xoff = static_cast<long long>(row) * job.x_ld + head * hd + l * 8;
+            ooff[it] = static_cast<long long>(row) * job.out_ld + head * hd + l * 8;
+            v[it] = live[it] ? *reinterpret_cast<const uint4*>(xin + xoff) : make_uint4(0, 0, 0, 0);
+            if (job.cos != nullptr) {
+                const long long t = static_cast<long long>(job.rope_row0 + row) * half + l * 4;
+                cs[it] = __ldg(reinterpret_cast<const float4*>(job.cos + t));
+                sn[it] = __ldg(reinterpret_cast<const float4*>(job.sin + t));
+            }
+        }
+#pragma unroll
+        for (int it = 0; it < kUnroll; ++it) {
+            float2 p[4];
+            p[0] = unpack2<kBf16>(v[it].x);
+            p[1] = unpack2<kBf16>(v[it].y);
+            p[2] = unpack2<kBf16>(v[it].z);
+            p[3] = unpack2<kBf16>(v[it].w);
+            if (job.gain != nullptr) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) ss += p[i].x * p[i].x + p[i].y * p[i].y;
+#pragma unroll
+                for (int o = kLpu / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float inv = rsqrtf(ss / static_cast<float>(hd) + a.eps);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    p[i].x = p[i].x * inv * g[2 * i];
+                    p[i].y = p[i].y * inv * g[2 * i + 1];
+                }
+            }
+            if (job.cos != nullptr) {
+                const float c[4] = {cs[it].x, cs[it].y, cs[it].z, cs[it].w};
+                const float s[4] = {sn[it].x, sn[it].y, sn[it].z, sn[it].w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float ra = p[i].x * c[i] - p[i].y * s[i];
+                    const float rb = p[i].x * s[i] + p[i].y * c[i];
+                    p[i].x = ra;
+                    p[i].y = rb;
+                }
+            }
+            if (live[it]) {
+                uint4 w;
+                w.x = pack2<kBf16>(p[0].x, p[0].y);
+                w.y = pack2<kBf16>(p[1].x, p[1].y);
+                w.z = pack2<kBf16>(p[2].x, p[2].y);
+                w.w = pack2<kBf16>(p[3].x, p[3].y);
+                *reinterpret_cast<uint4*>(xout + ooff[it]) = w;
+            }
+        }
+    }
+}
+
+template <bool kBf16>
+cudaError_t launch_vec(const NormRopeArgs& a, int lpu, dim3 grid, cudaStream_t stream) {
+    switch (lpu) {
+        case 1: norm_rope_vec_kernel<kBf16, 1><<<grid, 256, 0, stream>>>(a); break;
+        case 2: norm_rope_vec_kernel<kBf16, 2><<<grid, 256, 0, stream>>>(a); break;
+        case 4: norm_rope_vec_kernel<kBf16, 4><<<grid, 256, 0, stream>>>(a); break;
+        case 8: norm_rope_vec_kernel<kBf16, 8><<<grid, 256, 0, stream>>>(a); break;
+        case 16: norm_rope_vec_kernel<kBf16, 16><<<grid, 256, 0, stream>>>(a); break;
+        default: norm_rope_vec_kernel<kBf16, 32><<<grid, 256, 0, stream>>>(a); break;
+    }
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_norm_rope(const NormRopeArgs& a, bool bf16, cudaStream_t stream) {
@@ -125,6 +236,29 @@ cudaError_t launch_norm_rope(const NormRopeArgs& a, bool bf16, cudaStream_t stre
     for (int i = 0; i < a.n_jobs; ++i) {
         const long long u = static_cast<long long>(a.job[i].rows) * a.num_heads;
         if (u > max_units) max_units = u;
+    }
+    // Vector path when every job is 16-byte aligned and the head is a
+    // power-of-two number of 8-element slots.
+    const int hd = a.head_dim;
+    bool vec = a.pair_mode == 0 && hd % 8 == 0 && ((hd / 8) & (hd / 8 - 1)) == 0 && hd <= 256;
+    for (int i = 0; i < a.n_jobs && vec; ++i) {
+        const NormRopeJobDev& j = a.job[i];
+        if ((reinterpret_cast<uintptr_t>(j.x) & 15u) || (reinterpret_cast<uintptr_t>(j.out) & 15u) ||
+            (j.x_ld & 7) || (j.out_ld & 7))
+            vec = false;
+        if (j.cos != nullptr && ((reinterpret_cast<uintptr_t>(j.cos) & 15u) ||
+                                 (reinterpret_cast<uintptr_t>(j.sin) & 15u) || ((hd / 2) & 3)))
+            vec = false;
+    }
+    if (vec) {
+        const int lpu = hd / 8;
+        const long long units_per_cta = 8LL * 4 * (32 / lpu);
+        long long blocks = (max_units + units_per_cta - 1) / units_per_cta;
+        const long long cap = 148LL * 8;
+        if (blocks > cap) blocks = cap;
+        if (blocks < 1) blocks = 1;
+        dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.n_jobs));
+        return bf16 ? launch_vec<true>(a, lpu, grid, stream) : launch_vec<false>(a, lpu, grid, stream);
     }
     long long blocks = (max_units + kNormWarps - 1) / kNormWarps;
     const long long cap = 148LL * 16;  // 16 resident 256-thread CTAs per SM

@@ -33,6 +33,7 @@ struct SdpaLaunch {
     int batch;
     int head_dim;
     bool bf16;
+    int emu;   // exponentials per 8 evaluated by polynomial (0, 2, 4 or 6)
 };
 
 cudaError_t launch_sdpa_tc05(const SdpaLaunch& L, cudaStream_t stream);
@@ -96,5 +97,25 @@ struct LinearAttnArgs {
 };
 cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
                                const CUtensorMap& tmV, int cluster_size, cudaStream_t stream);
+
+// Device-side RoPE table build.
+constexpr int kMaxRopeSegments = 64;
+struct RopeTableArgs {
+    int flux;      // 1: Flux rule (text identity, image (0, i, j)); 0: Qwen-Image running position
+    int rows;
+    int half;
+    int n_axes;
+    int axes[4];
+    float theta;
+    int n_seg;
+    int seg_kind[kMaxRopeSegments];   // 0 text, 1 image
+    int seg_row0[kMaxRopeSegments];
+    int seg_pos0[kMaxRopeSegments];   // running position at the segment start
+    int seg_h[kMaxRopeSegments];
+    int seg_w[kMaxRopeSegments];
+    float* cos_out;
+    float* sin_out;
+};
+cudaError_t launch_rope_tables(const RopeTableArgs& a, cudaStream_t stream);
 
 }  // namespace bdattn

@@ -1,11 +1,13 @@
 // Softmax attention forward for head_dim 64 / 128 on the sm_100a tensor cores.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and walks the key
-// tiles (128 keys each).  Roles (10 warps):
-//   warps 0-3 : softmax of query tile 0   (one thread per query row)
-//   warps 4-7 : softmax of query tile 1
-//   warp  8   : issues every tcgen05.mma (one lane), owns the TMEM allocation
-//   warp  9   : TMA producer for Q, K and V tiles (one lane)
+// tiles (128 keys each).  Roles (12 warps, three warpgroups):
+//   warps 0-3  : softmax of query tile 0   (one thread per query row)
+//   warps 4-7  : softmax of query tile 1
+//   warp  8    : issues every tcgen05.mma (one lane), owns the TMEM allocation
+//   warp  9    : TMA producer for Q, K and V tiles (one lane)
+//   warps 10-11: idle (they complete the third warpgroup so that registers
+//                can be moved to the softmax warpgroups with setmaxnreg)
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+HD)
 // O1 [256+HD,256+2HD).  P (the exponentiated scores, 16-bit, two per column)
 // is written back over the first 64 columns of its S tile and consumed from
@@ -17,6 +19,13 @@
 // running maximum is only raised when it grew by more than 2^8 (the factor
 // is carried by P and cancels in O / l), which makes the O rescale rare; the
 // rescale is done in tensor memory by the softmax warps themselves.
+//
+// The softmax is the co-bottleneck of this kernel (16 MUFU results per clock
+// per SM against 8192 dense BF16 FLOP per clock), so its arithmetic is packed
+// two floats per instruction (fma/add .f32x2), the row maximum uses the
+// three-input max, and a compile-time share of the exponentials is evaluated
+// on the FMA pipe with a degree-3 polynomial instead of ex2.approx (relative
+// error 1.0e-4, below the 2^-9 rounding of P to BF16).
 //
 // Arithmetic follows the attention core of dit::joint_attention_traced
 // (src/dit/common.cpp:246-305): scale 1/sqrt(hd), stable softmax,
@@ -30,8 +39,10 @@ namespace {
 
 constexpr int kBM = 128;           // query rows per tile
 constexpr int kBN = 128;           // keys per tile
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;
 constexpr int kChunkBytes = 128 * 128;  // one 64-column (128 B) x 128-row TMA box
+constexpr int kRegsSoftmax = 216;
+constexpr int kRegsOther = 64;
 
 template <int HD>
 struct Cfg {
@@ -66,7 +77,82 @@ __device__ __forceinline__ TileInfo kv_tile(const SdpaDevArgs& a, int t) {
     return ti;
 }
 
-template <int HD, bool kBf16>
+// ------------------------------------------------------- packed FP32 math
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1)
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1,
+                                      float c0, float c1) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "mov.b64 rc, {%6, %7};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "add.rn.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// round-towards-minus-infinity packed add (used to take floor(x) below)
+__device__ __forceinline__ void fadd2_rm(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "add.rm.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// 2^x for two values on the FMA pipe: x = n + f with n = floor(x), f in [0,1);
+// 2^f by a degree-3 polynomial fitted on [0,1) with p(0) = 1 and p(1) = 2
+// (max relative error 1.03e-4), then n is added into the exponent field.
+// x is clamped to >= -127 (results below 2^-127 are zero for this purpose).
+__device__ __forceinline__ void exp2_poly2(float& p0, float& p1, float x0, float x1) {
+    constexpr float kMagic = 12582912.0f;  // 2^23 + 2^22: integers sit in the low mantissa bits
+    constexpr float kC1 = 0.6954243183135986f, kC2 = 0.2263076901435852f, kC3 = 0.07826796919107437f;
+    x0 = fmaxf(x0, -127.0f);
+    x1 = fmaxf(x1, -127.0f);
+    float r0, r1, b0, b1, f0, f1;
+    fadd2_rm(r0, r1, x0, x1, kMagic, kMagic);
+    fadd2(b0, b1, r0, r1, -kMagic, -kMagic);
+    fadd2(f0, f1, x0, x1, -b0, -b1);
+    float q0, q1;
+    ffma2(q0, q1, f0, f1, kC3, kC3, kC2, kC2);
+    ffma2(q0, q1, q0, q1, f0, f1, kC1, kC1);
+    ffma2(q0, q1, q0, q1, f0, f1, 1.0f, 1.0f);
+    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
+    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
+}
+
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+// HOOKS: key_mask / key_scale / val_scale are honoured (slower softmax path).
+// EMU  : of every 8 consecutive exponentials, EMU are evaluated by polynomial.
+template <int HD, bool kBf16, bool kHooks, int kEmu>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                  const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
@@ -139,6 +225,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 
     if (warp < 8) {
         // ------------------------------------------------ softmax + epilogue
+        setmaxnreg_inc<kRegsSoftmax>();
         const int t = warp >> 2;
         const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
         const uint32_t tS = tmem_base + lane_base + static_cast<uint32_t>(t * kBN);
@@ -163,10 +250,12 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             tmem_wait_ld();
 
             const TileInfo ti = kv_tile(a, j);
-            if (a.key_scale != nullptr) {
+            if constexpr (kHooks) {
+                if (a.key_scale != nullptr) {
 #pragma unroll
-                for (int c = 0; c < kBN; ++c) {
-                    if (c < ti.valid) s[c] *= __ldg(a.key_scale + ti.kbase + c);
+                    for (int c = 0; c < kBN; ++c) {
+                        if (c < ti.valid) s[c] *= __ldg(a.key_scale + ti.kbase + c);
+                    }
                 }
             }
             int lim = ti.valid - 1;
@@ -175,16 +264,29 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < kBN; ++c) s[c] = (c <= lim) ? s[c] : -INFINITY;
             }
-            if (a.key_mask != nullptr) {
+            if constexpr (kHooks) {
+                if (a.key_mask != nullptr) {
 #pragma unroll
-                for (int c = 0; c < kBN; ++c) {
-                    if (c < ti.valid && __ldg(a.key_mask + ti.kbase + c) == 0.0f) s[c] = -INFINITY;
+                    for (int c = 0; c < kBN; ++c) {
+                        if (c < ti.valid && __ldg(a.key_mask + ti.kbase + c) == 0.0f) s[c] = -INFINITY;
+                    }
                 }
             }
 
-            float mx = s[0];
+            // row maximum: four independent chains of three-input max
+            float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+            float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-            for (int c = 1; c < kBN; ++c) mx = fmaxf(mx, s[c]);
+            for (int c = 12; c + 7 < kBN; c += 8) {
+                mx0 = max3(mx0, s[c], s[c + 1]);
+                mx1 = max3(mx1, s[c + 2], s[c + 3]);
+                mx2 = max3(mx2, s[c + 4], s[c + 5]);
+                mx3 = max3(mx3, s[c + 6], s[c + 7]);
+            }
+            // 12 + 8*14 = 124: four scores left
+            mx0 = max3(mx0, s[124], s[125]);
+            mx1 = max3(mx1, s[126], s[127]);
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = fmaxf(m_ref, mx);
             const bool grow = (m_new - m_ref) * sl2 > 8.0f;
             if (__any_sync(0xffffffffu, grow)) {
@@ -211,25 +313,36 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             }
             const float m_use = (m_ref == -INFINITY) ? 0.0f : m_ref;
             const float neg_ms = -m_use * sl2;
-            float rs = 0.0f;
+            // p = 2^(s * scale_log2 - m * scale_log2); row sum in four packed chains
+            float rs[8];
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                uint32_t pk[32];
+            for (int i = 0; i < 8; ++i) rs[i] = 0.0f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int c0 = ch * 64 + 2 * i;
-                    float p0 = fast_exp2(fmaf(s[c0], sl2, neg_ms));
-                    float p1 = fast_exp2(fmaf(s[c0 + 1], sl2, neg_ms));
-                    rs += p0 + p1;
-                    if (a.val_scale != nullptr) {
-                        if (c0 < ti.valid) p0 *= __ldg(a.val_scale + ti.kbase + c0);
-                        if (c0 + 1 < ti.valid) p1 *= __ldg(a.val_scale + ti.kbase + c0 + 1);
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const int c0 = ch * 32 + 2 * i;
+                    float x0, x1, p0, p1;
+                    ffma2(x0, x1, s[c0], s[c0 + 1], sl2, sl2, neg_ms, neg_ms);
+                    if ((i & 3) < kEmu / 2) {
+                        exp2_poly2(p0, p1, x0, x1);
+                    } else {
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                    }
+                    fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
+                    if constexpr (kHooks) {
+                        if (a.val_scale != nullptr) {
+                            if (c0 < ti.valid) p0 *= __ldg(a.val_scale + ti.kbase + c0);
+                            if (c0 + 1 < ti.valid) p1 *= __ldg(a.val_scale + ti.kbase + c0 + 1);
+                        }
                     }
                     pk[i] = pack2<kBf16>(p0, p1);
                 }
-                tmem_st32(tS + ch * 32, pk);
+                tmem_st16(tS + ch * 16, pk);
             }
-            l_sum += rs;
+            l_sum += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(&p_full[t]);
@@ -273,116 +386,119 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 }
             }
         }
-    } else if (warp == 8) {
-        // ------------------------------------------------------ MMA issuer
-        constexpr int kFmt = kBf16 ? 1 : 0;
-        constexpr uint32_t idesc_qk = make_idesc_f16(kFmt, kBM, kBN, 0, 0);
-        constexpr uint32_t idesc_pv = make_idesc_f16(kFmt, kBM, HD, 0, 1);
-        const uint32_t q_base = smem_u32(smem_q);
-        const uint32_t kv_base = smem_u32(smem_kv);
+    } else {
+        setmaxnreg_dec<kRegsOther>();
+        if (warp == 8) {
+            // -------------------------------------------------- MMA issuer
+            constexpr int kFmt = kBf16 ? 1 : 0;
+            constexpr uint32_t idesc_qk = make_idesc_f16(kFmt, kBM, kBN, 0, 0);
+            constexpr uint32_t idesc_pv = make_idesc_f16(kFmt, kBM, HD, 0, 1);
+            const uint32_t q_base = smem_u32(smem_q);
+            const uint32_t kv_base = smem_u32(smem_kv);
 
-        auto issue_qk = [&](int t, int slot) {
-            const uint32_t qa = q_base + t * C::kQBytes;
-            const uint32_t kb = kv_base + slot * C::kTileBytes;
+            auto issue_qk = [&](int t, int slot) {
+                const uint32_t qa = q_base + t * C::kQBytes;
+                const uint32_t kb = kv_base + slot * C::kTileBytes;
 #pragma unroll
-            for (int kk = 0; kk < HD / 16; ++kk) {
-                const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
-                umma_ss(tmem_base + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024),
-                        make_smem_desc_sw128(kb + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
-            }
-        };
-        auto issue_pv = [&](int t, int slot, bool acc) {
-            const uint32_t vb = kv_base + slot * C::kTileBytes;
-#pragma unroll
-            for (int kk = 0; kk < kBN / 16; ++kk) {
-                umma_ts(tmem_base + 256 + t * HD, tmem_base + t * kBN + kk * 8,
-                        make_smem_desc_sw128(vb + kk * 2048, kChunkBytes, 1024), idesc_pv,
-                        (acc || kk > 0) ? 1u : 0u);
-            }
-        };
-
-        bool ok = n_kv > 0;
-        if (ok) ok = mbar_wait(&q_full[0], 0) && mbar_wait(&q_full[1], 0);
-        if (ok) ok = mbar_wait(&kv_full[0], 0);
-        if (ok) {
-            tc_fence_after();
-            if (lane == 0) {
-                issue_qk(0, 0);
-                umma_commit(&s_full[0]);
-                issue_qk(1, 0);
-                umma_commit(&s_full[1]);
-                umma_commit(&kv_empty[0]);
-            }
-            __syncwarp();
-        }
-        for (int j = 0; ok && j < n_kv; ++j) {
-            const int iv = 2 * j + 1;
-            const int vslot = iv % ST;
-            ok = mbar_wait(&kv_full[vslot], static_cast<uint32_t>((iv / ST) & 1));
-            if (!ok) break;
-            const int ik = 2 * j + 2;
-            const int kslot = ik % ST;
-            for (int t = 0; t < 2 && ok; ++t) {
-                ok = mbar_wait(&p_full[t], static_cast<uint32_t>(j & 1));
-                if (!ok) break;
-                if (t == 0 && j + 1 < n_kv) {
-                    ok = mbar_wait(&kv_full[kslot], static_cast<uint32_t>((ik / ST) & 1));
-                    if (!ok) break;
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * kChunkBytes + (kk & 3) * 32;
+                    umma_ss(tmem_base + t * kBN, make_smem_desc_sw128(qa + off, 16, 1024),
+                            make_smem_desc_sw128(kb + off, 16, 1024), idesc_qk, kk > 0 ? 1u : 0u);
                 }
+            };
+            auto issue_pv = [&](int t, int slot, bool acc) {
+                const uint32_t vb = kv_base + slot * C::kTileBytes;
+#pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk) {
+                    umma_ts(tmem_base + 256 + t * HD, tmem_base + t * kBN + kk * 8,
+                            make_smem_desc_sw128(vb + kk * 2048, kChunkBytes, 1024), idesc_pv,
+                            (acc || kk > 0) ? 1u : 0u);
+                }
+            };
+
+            bool ok = n_kv > 0;
+            if (ok) ok = mbar_wait(&q_full[0], 0) && mbar_wait(&q_full[1], 0);
+            if (ok) ok = mbar_wait(&kv_full[0], 0);
+            if (ok) {
                 tc_fence_after();
                 if (lane == 0) {
-                    issue_pv(t, vslot, j > 0);
-                    umma_commit(&pv_done[t]);
-                    if (j + 1 < n_kv) {
-                        issue_qk(t, kslot);
-                        umma_commit(&s_full[t]);
-                        if (t == 1) umma_commit(&kv_empty[kslot]);
-                    }
+                    issue_qk(0, 0);
+                    umma_commit(&s_full[0]);
+                    issue_qk(1, 0);
+                    umma_commit(&s_full[1]);
+                    umma_commit(&kv_empty[0]);
                 }
                 __syncwarp();
             }
-            if (ok && lane == 0) umma_commit(&kv_empty[vslot]);
+            for (int j = 0; ok && j < n_kv; ++j) {
+                const int iv = 2 * j + 1;
+                const int vslot = iv % ST;
+                ok = mbar_wait(&kv_full[vslot], static_cast<uint32_t>((iv / ST) & 1));
+                if (!ok) break;
+                const int ik = 2 * j + 2;
+                const int kslot = ik % ST;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    ok = mbar_wait(&p_full[t], static_cast<uint32_t>(j & 1));
+                    if (!ok) break;
+                    if (t == 0 && j + 1 < n_kv) {
+                        ok = mbar_wait(&kv_full[kslot], static_cast<uint32_t>((ik / ST) & 1));
+                        if (!ok) break;
+                    }
+                    tc_fence_after();
+                    if (lane == 0) {
+                        issue_pv(t, vslot, j > 0);
+                        umma_commit(&pv_done[t]);
+                        if (j + 1 < n_kv) {
+                            issue_qk(t, kslot);
+                            umma_commit(&s_full[t]);
+                            if (t == 1) umma_commit(&kv_empty[kslot]);
+                        }
+                    }
+                    __syncwarp();
+                }
+                if (ok && lane == 0) umma_commit(&kv_empty[vslot]);
+                __syncwarp();
+            }
+        } else if (warp == 9) {
+            // ------------------------------------------------ TMA producer
+            if (lane == 0 && n_kv > 0) {
+                const CUtensorMap* mq = qseg ? &tmQ1 : &tmQ0;
+                for (int t = 0; t < 2; ++t) {
+                    mbar_arrive_expect_tx(&q_full[t], C::kQBytes);
+                    for (int c = 0; c < C::kChunks; ++c) {
+                        tma_load_3d(smem_q + t * C::kQBytes + c * kChunkBytes, mq, &q_full[t],
+                                    head * HD + c * 64, qrow0 + t * kBM, batch);
+                    }
+                }
+                int issued = 0;
+                bool ok = true;
+                for (int i = 0; i < 2 * n_kv; ++i) {
+                    const int slot = i % ST;
+                    if (i >= ST) {
+                        ok = mbar_wait(&kv_empty[slot], static_cast<uint32_t>(((i / ST) - 1) & 1));
+                        if (!ok) break;
+                    }
+                    const TileInfo ti = kv_tile(a, i >> 1);
+                    const CUtensorMap* m = (i & 1) ? (ti.seg ? &tmV1 : &tmV0) : (ti.seg ? &tmK1 : &tmK0);
+                    mbar_arrive_expect_tx(&kv_full[slot], C::kTileBytes);
+                    for (int c = 0; c < C::kChunks; ++c) {
+                        tma_load_3d(smem_kv + slot * C::kTileBytes + c * kChunkBytes, m, &kv_full[slot],
+                                    head * HD + c * 64, ti.row0, batch);
+                    }
+                    issued = i + 1;
+                }
+                if (!ok) {
+                    // Unwinding after a wait ran out: let the copies already in
+                    // flight land before the CTA gives its shared memory back.
+                    mbar_wait(&q_full[0], 0);
+                    mbar_wait(&q_full[1], 0);
+                    for (int i = max(0, issued - ST); i < issued; ++i) {
+                        mbar_wait(&kv_full[i % ST], static_cast<uint32_t>((i / ST) & 1));
+                    }
+                }
+            }
             __syncwarp();
         }
-    } else {
-        // ---------------------------------------------------- TMA producer
-        if (lane == 0 && n_kv > 0) {
-            const CUtensorMap* mq = qseg ? &tmQ1 : &tmQ0;
-            for (int t = 0; t < 2; ++t) {
-                mbar_arrive_expect_tx(&q_full[t], C::kQBytes);
-                for (int c = 0; c < C::kChunks; ++c) {
-                    tma_load_3d(smem_q + t * C::kQBytes + c * kChunkBytes, mq, &q_full[t],
-                                head * HD + c * 64, qrow0 + t * kBM, batch);
-                }
-            }
-            int issued = 0;
-            bool ok = true;
-            for (int i = 0; i < 2 * n_kv; ++i) {
-                const int slot = i % ST;
-                if (i >= ST) {
-                    ok = mbar_wait(&kv_empty[slot], static_cast<uint32_t>(((i / ST) - 1) & 1));
-                    if (!ok) break;
-                }
-                const TileInfo ti = kv_tile(a, i >> 1);
-                const CUtensorMap* m = (i & 1) ? (ti.seg ? &tmV1 : &tmV0) : (ti.seg ? &tmK1 : &tmK0);
-                mbar_arrive_expect_tx(&kv_full[slot], C::kTileBytes);
-                for (int c = 0; c < C::kChunks; ++c) {
-                    tma_load_3d(smem_kv + slot * C::kTileBytes + c * kChunkBytes, m, &kv_full[slot],
-                                head * HD + c * 64, ti.row0, batch);
-                }
-                issued = i + 1;
-            }
-            if (!ok) {
-                // Unwinding after a wait ran out: let the copies already in
-                // flight land before the CTA gives its shared memory back.
-                mbar_wait(&q_full[0], 0);
-                mbar_wait(&q_full[1], 0);
-                for (int i = max(0, issued - ST); i < issued; ++i) {
-                    mbar_wait(&kv_full[i % ST], static_cast<uint32_t>((i / ST) & 1));
-                }
-            }
-        }
-        __syncwarp();
     }
 
     tc_fence_before();
@@ -393,10 +509,10 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     }
 }
 
-template <int HD, bool kBf16>
+template <int HD, bool kBf16, bool kHooks, int kEmu>
 cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     using C = Cfg<HD>;
-    auto kern = sdpa_tc05_kernel<HD, kBf16>;
+    auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks, kEmu>;
     static thread_local int configured_dev = -1;
     int dev = 0;
     cudaGetDevice(&dev);
@@ -413,11 +529,24 @@ cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     return cudaGetLastError();
 }
 
+template <int HD, bool kBf16>
+cudaError_t launch_hd(const SdpaLaunch& L, cudaStream_t stream) {
+    const bool hooks = L.args.key_mask != nullptr || L.args.key_scale != nullptr ||
+                       L.args.val_scale != nullptr;
+    if (hooks) return launch_t<HD, kBf16, true, 0>(L, stream);
+    switch (L.emu) {
+        case 0: return launch_t<HD, kBf16, false, 0>(L, stream);
+        case 2: return launch_t<HD, kBf16, false, 2>(L, stream);
+        case 6: return launch_t<HD, kBf16, false, 6>(L, stream);
+        default: return launch_t<HD, kBf16, false, 4>(L, stream);
+    }
+}
+
 }  // namespace
 
 cudaError_t launch_sdpa_tc05(const SdpaLaunch& L, cudaStream_t stream) {
-    if (L.head_dim == 128) return L.bf16 ? launch_t<128, true>(L, stream) : launch_t<128, false>(L, stream);
-    if (L.head_dim == 64) return L.bf16 ? launch_t<64, true>(L, stream) : launch_t<64, false>(L, stream);
+    if (L.head_dim == 128) return L.bf16 ? launch_hd<128, true>(L, stream) : launch_hd<128, false>(L, stream);
+    if (L.head_dim == 64) return L.bf16 ? launch_hd<64, true>(L, stream) : launch_hd<64, false>(L, stream);
     return cudaErrorInvalidValue;
 }
 

@@ -152,6 +152,42 @@ typedef struct bdattn_norm_rope_job {
 int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype, int num_heads,
                         int head_dim, float eps, int pair_mode, bdattn_stream_t stream);
 
+/* ------------------------------------------------------- RoPE tables
+ * FP32 cos/sin tables (rows, head_dim/2) built on the device, replacing the
+ * host loops + upload the reference runs every forward.
+ *
+ * bdattn_rope_tables_flux replaces dit::build_axial_rope_tables
+ * (src/dit/common.cpp:116-184, called at src/dit/flux.cpp:760): rows =
+ * txt_len + hp*wp; text rows are the identity rotation; image token (i, j)
+ * sits at axial position (0, i, j); axis a owns axes_dims[a]/2 pairs with
+ * omega = theta^(-2p/axes_dims[a]).  Errors keep the reference's messages
+ * ("build_axial_rope_tables: axes_dims_rope must sum to head_dim").
+ *
+ * bdattn_rope_tables_qwen replaces
+ * QwenImage21Transformer2DModel::build_rope_tables_
+ * (src/dit/qwenimage21_forward.cpp:124-200): a running position walks the
+ * prefix segments and then the (hp, wp) target image; a text token sits at
+ * (p, p, p); an image block freezes the frame axis at p, centres its grid on
+ * zero and advances p by max(h, w).  bdattn_rope_rows_qwen returns the row
+ * count of that table (host-only helper).
+ */
+typedef struct bdattn_rope_segment {
+    int kind;      /* 0 = text (n_tokens), 1 = image (h x w) */
+    int n_tokens;
+    int h;
+    int w;
+} bdattn_rope_segment;
+
+int bdattn_rope_tables_flux(int txt_len, int hp, int wp, int head_dim, const int* axes_dims,
+                            int n_axes, float theta, float* cos, float* sin,
+                            bdattn_stream_t stream);
+
+int bdattn_rope_rows_qwen(const bdattn_rope_segment* prefix, int n_prefix, int hp, int wp);
+
+int bdattn_rope_tables_qwen(const bdattn_rope_segment* prefix, int n_prefix, int hp, int wp,
+                            int head_dim, const int* axes_dims3, float theta, float* cos,
+                            float* sin, bdattn_stream_t stream);
+
 /* ------------------------------------------------ ReLU linear attention
  * Sana self-attention core.  Replaces the op sequence of
  * SanaDenoiser::self_attention_ (src/dit/sana.cpp:521-586; FP32 statement of
