@@ -40,7 +40,7 @@ WORKLOADS = {
 }
 # dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_tc05_kernel launch
 # on the flux1024 workload, from the ncu capture summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"flux1024": None}
+NCU_TRAFFIC_BYTES = {"flux1024": 84.99e6 + 6.07e6}
 
 
 def measured_peaks():

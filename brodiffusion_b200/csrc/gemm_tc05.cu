@@ -1,0 +1,226 @@
+// Linear layers on the sm_100a tensor cores:  C[M,N] = A[M,K] . B[N,K]^T (+ bias)
+// with 16-bit operands, FP32 accumulation in tensor memory and a fused
+// epilogue.  Weights are stored (out_features, in_features) as in the
+// reference (src/unet_blocks.cpp:264-271), so both operands are K-major and
+// are staged by TMA with the 128-byte swizzle.
+//
+// Up to three independent problems share one launch (blockIdx.z): the Q, K
+// and V projections of one attention call.  A CTA computes one 128-row x
+// n_tile-column tile:
+//   warp 0     TMA producer (A tile 128 x 64, B tile n_tile x 64 per K block)
+//   warp 1     tcgen05.mma issuer, owns the TMEM allocation
+//   warps 2-5  epilogue: tcgen05.ld -> bias / GEGLU -> 16-byte stores
+// Tiles may be head-aligned: tile t starts at weight row t * n_step and its
+// n_valid columns land at output column t * c_step, zero-filled up to c_fill.
+// That writes Q/K/V with every head padded to the width the attention kernel
+// takes (40 -> 64, 80 -> 128) without a separate padding pass.
+//
+// GEGLU mode (src/fused_transformer.cu:89-92,275-282): a second B tile from
+// weight row n0 + D_out feeds a second accumulator and the epilogue stores
+// value * gelu_exact(gate), so the (B, 2*D_out) intermediate never exists.
+#include "sdpa_internal.h"
+#include "tc05.cuh"
+
+namespace bdattn {
+namespace {
+
+constexpr int kGemmThreads = 192;
+constexpr int kGemmStages = 4;
+constexpr int kGemmABytes = 128 * 64 * 2;   // A stage
+constexpr int kGemmBBytes = 128 * 64 * 2;   // B stage (n_tile <= 128)
+constexpr int kGemmStageBytes = kGemmABytes + 2 * kGemmBBytes;   // + gate tile
+constexpr int kGemmSmemBytes = kGemmStages * kGemmStageBytes + 256 + 1024;
+
+template <bool kBf16>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmA1,
+                 const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB0,
+                 const __grid_constant__ CUtensorMap tmB1, const __grid_constant__ CUtensorMap tmB2,
+                 const GemmArgs g) {
+    const int z = blockIdx.z;
+    const GemmProblem& p = z == 0 ? g.p[0] : (z == 1 ? g.p[1] : g.p[2]);
+    const CUtensorMap* tmA = z == 0 ? &tmA0 : (z == 1 ? &tmA1 : &tmA2);
+    const CUtensorMap* tmB = z == 0 ? &tmB0 : (z == 1 ? &tmB1 : &tmB2);
+    const int tile_n = blockIdx.x;
+    const int tile_m = blockIdx.y;
+    if (tile_n >= p.tiles_n || tile_m >= p.tiles_m) return;
+
+    extern __shared__ uint8_t gemm_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kGemmStages * kGemmStageBytes);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + kGemmStages;
+    uint64_t* acc_done = empty + kGemmStages;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int k_blocks = (p.K + 63) / 64;
+    const int n0 = tile_n * p.n_step;
+    const int m0 = tile_m * 128;
+    const bool geglu = p.geglu_offset > 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kGemmStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_done, 1);
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 256);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t bytes = kGemmABytes + (geglu ? 2u : 1u) * static_cast<uint32_t>(p.n_tile) * 128u;
+            bool ok = true;
+            int issued = 0;
+            for (int kb = 0; kb < k_blocks; ++kb) {
+                const int s = kb % kGemmStages;
+                if (kb >= kGemmStages) {
+                    ok = mbar_wait(&empty[s], static_cast<uint32_t>(((kb / kGemmStages) - 1) & 1));
+                    if (!ok) break;
+                }
+                uint8_t* st = smem + s * kGemmStageBytes;
+                mbar_arrive_expect_tx(&full[s], bytes);
+                tma_load_2d(st, tmA, &full[s], kb * 64, m0);
+                tma_load_2d(st + kGemmABytes, tmB, &full[s], kb * 64, n0);
+                if (geglu) tma_load_2d(st + kGemmABytes + kGemmBBytes, tmB, &full[s], kb * 64, n0 + p.geglu_offset);
+                issued = kb + 1;
+            }
+            if (!ok) {
+                for (int kb = max(0, issued - kGemmStages); kb < issued; ++kb)
+                    mbar_wait(&full[kb % kGemmStages], static_cast<uint32_t>((kb / kGemmStages) & 1));
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        const uint32_t idesc = make_idesc_f16(kBf16 ? 1 : 0, 128, p.n_tile, 0, 0);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; ++kb) {
+            const int s = kb % kGemmStages;
+            ok = mbar_wait(&full[s], static_cast<uint32_t>((kb / kGemmStages) & 1));
+            if (!ok) break;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t ab = smem_u32(smem + s * kGemmStageBytes);
+                const uint32_t bb = ab + kGemmABytes;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    const uint64_t ad = make_smem_desc_sw128(ab + kk * 32, 16, 1024);
+                    umma_ss(tmem_base, ad, make_smem_desc_sw128(bb + kk * 32, 16, 1024), idesc,
+                            (kb > 0 || kk > 0) ? 1u : 0u);
+                    if (geglu)
+                        umma_ss(tmem_base + 128, ad, make_smem_desc_sw128(bb + kGemmBBytes + kk * 32, 16, 1024),
+                                idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);
+                if (kb == k_blocks - 1) umma_commit(acc_done);
+            }
+            __syncwarp();
+        }
+    } else {
+        // epilogue: warp w reads TMEM lanes 32 * (w % 4) ..
+        const int q = warp & 3;
+        const int row = m0 + q * 32 + lane;
+        bool ok = mbar_wait(acc_done, 0);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
+        const uint32_t tacc = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+        const long long c0 = static_cast<long long>(tile_n) * p.c_step;
+        uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + c0;
+        const int n_valid = min(p.n_valid, p.N - n0);
+        if (ok) {
+            for (int c = 0; c < p.c_fill; c += 32) {
+                uint32_t v[32], gt[32];
+                if (c < p.n_tile) {
+                    tmem_ld32(tacc + c, v);
+                    if (geglu) tmem_ld32(tacc + 128 + c, gt);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0u;
+                }
+                float f[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int col = c + i;
+                    float x = __uint_as_float(v[i]);
+                    if (col < n_valid) {
+                        if (p.bias != nullptr) {
+                            const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + col];
+                            x += kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                       : __half2float(*reinterpret_cast<const __half*>(&b));
+                        }
+                        if (geglu) {
+                            float gate = __uint_as_float(gt[i]);
+                            if (p.bias != nullptr) {
+                                const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + p.geglu_offset + col];
+                                gate += kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                              : __half2float(*reinterpret_cast<const __half*>(&b));
+                            }
+                            x *= 0.5f * gate * (1.0f + erff(gate * 0.7071067811865475f));
+                        }
+                    } else {
+                        x = 0.0f;
+                    }
+                    f[i] = x;
+                }
+                if (row < p.M) {
+#pragma unroll
+                    for (int v8 = 0; v8 < 4; ++v8) {
+                        if (c + v8 * 8 < p.c_fill) {
+                            uint4 w;
+                            w.x = pack2<kBf16>(f[v8 * 8 + 0], f[v8 * 8 + 1]);
+                            w.y = pack2<kBf16>(f[v8 * 8 + 2], f[v8 * 8 + 3]);
+                            w.z = pack2<kBf16>(f[v8 * 8 + 4], f[v8 * 8 + 5]);
+                            w.w = pack2<kBf16>(f[v8 * 8 + 6], f[v8 * 8 + 7]);
+                            *reinterpret_cast<uint4*>(crow + c + v8 * 8) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_tc05(const GemmLaunch& L, cudaStream_t stream) {
+    int tn = 0, tm = 0;
+    for (int i = 0; i < L.n_problems; ++i) {
+        tn = L.args.p[i].tiles_n > tn ? L.args.p[i].tiles_n : tn;
+        tm = L.args.p[i].tiles_m > tm ? L.args.p[i].tiles_m : tm;
+    }
+    dim3 grid(static_cast<unsigned>(tn), static_cast<unsigned>(tm), static_cast<unsigned>(L.n_problems));
+    cudaError_t e;
+    if (L.bf16) {
+        e = cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+        if (e != cudaSuccess) return e;
+        gemm_tc05_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
+            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], L.args);
+    } else {
+        e = cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+        if (e != cudaSuccess) return e;
+        gemm_tc05_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
+            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], L.args);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace bdattn
