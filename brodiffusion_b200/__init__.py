@@ -64,6 +64,22 @@ class RopeSegment(C.Structure):
     _fields_ = [("kind", C.c_int), ("n_tokens", C.c_int), ("h", C.c_int), ("w", C.c_int)]
 
 
+class QkvoParams(C.Structure):
+    """Mirror of ``bdattn_qkvo_params`` (include/bdattn.h)."""
+    _fields_ = [
+        ("dtype", C.c_int), ("num_heads", C.c_int), ("inner_dim", C.c_int), ("causal", C.c_int),
+        ("x", C.c_void_p), ("x_rows", C.c_int), ("x_cols", C.c_int), ("x_ld", C.c_longlong),
+        ("ctx", C.c_void_p), ("ctx_rows", C.c_int), ("ctx_cols", C.c_int), ("ctx_ld", C.c_longlong),
+        ("wq", C.c_void_p), ("bq", C.c_void_p), ("wk", C.c_void_p), ("bk", C.c_void_p),
+        ("wv", C.c_void_p), ("bv", C.c_void_p), ("wo", C.c_void_p), ("bo", C.c_void_p),
+        ("k_cached", C.c_void_p), ("v_cached", C.c_void_p), ("kv_rows", C.c_int),
+        ("k_ld", C.c_longlong), ("v_ld", C.c_longlong),
+        ("key_mask", C.c_void_p),
+        ("out", C.c_void_p), ("out_cols", C.c_int), ("out_ld", C.c_longlong),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 _lib = None
 
 
@@ -98,6 +114,20 @@ def lib():
         L.bdattn_rope_tables_qwen.argtypes = [C.POINTER(RopeSegment), C.c_int, C.c_int, C.c_int,
                                               C.c_int, C.POINTER(C.c_int), C.c_float,
                                               C.c_void_p, C.c_void_p, C.c_void_p]
+        L.bdattn_qkvo_workspace_bytes.restype = C.c_size_t
+        L.bdattn_qkvo_workspace_bytes.argtypes = [C.c_int] * 4
+        L.bdattn_qkvo_fwd.argtypes = [C.POINTER(QkvoParams), C.c_void_p]
+        L.bdattn_project_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_longlong, C.c_void_p,
+                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                        C.c_longlong, C.c_int, C.c_int, C.c_void_p]
+        L.bdattn_linear_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int,
+                                        C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_longlong,
+                                        C.c_longlong, C.c_void_p]
+        L.bdattn_linear_geglu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
+        L.bdattn_add_inplace.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p]
+        L.bdattn_add_row_bias.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_longlong,
+                                          C.c_int, C.c_void_p]
         _lib = L
     return _lib
 
@@ -260,3 +290,73 @@ def linear_attn_relu_fwd(q, k, v, out, num_heads, head_dim, *, eps=1e-15, sz_in=
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), _dtype_code(q), B, num_heads,
         head_dim, n_tokens, ld, bs, eps, sz_in.data_ptr() if sz_in is not None else None, w_in,
         sz_out.data_ptr() if sz_out is not None else None, _stream(stream)))
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None else None
+
+
+def qkvo_workspace_bytes(q_rows, kv_rows, num_heads, head_dim) -> int:
+    return int(lib().bdattn_qkvo_workspace_bytes(q_rows, kv_rows, num_heads, head_dim))
+
+
+def qkvo_fwd(x, ctx, wq, wk, wv, wo, bo, num_heads, out, workspace, *, bq=None, bk=None, bv=None,
+             k_cached=None, v_cached=None, key_mask=None, causal=False, stream=None):
+    """``bdattn_qkvo_fwd``: the reference's flash_attention_qkvo_forward, or
+    flash_attention_q_with_kv_cached_forward when k_cached / v_cached are given."""
+    p = QkvoParams()
+    p.dtype = _dtype_code(x)
+    p.num_heads = num_heads
+    p.inner_dim = wq.shape[0]
+    p.causal = 1 if causal else 0
+    p.x, p.x_rows, p.x_cols, p.x_ld = x.data_ptr(), x.shape[0], x.shape[1], x.stride(0)
+    if ctx is not None:
+        p.ctx, p.ctx_rows, p.ctx_cols, p.ctx_ld = ctx.data_ptr(), ctx.shape[0], ctx.shape[1], ctx.stride(0)
+    p.wq, p.bq, p.wk, p.bk = _ptr(wq), _ptr(bq), _ptr(wk), _ptr(bk)
+    p.wv, p.bv, p.wo, p.bo = _ptr(wv), _ptr(bv), _ptr(wo), _ptr(bo)
+    if k_cached is not None:
+        p.k_cached, p.v_cached = k_cached.data_ptr(), v_cached.data_ptr()
+        p.kv_rows, p.k_ld, p.v_ld = k_cached.shape[0], k_cached.stride(0), v_cached.stride(0)
+    p.key_mask = _ptr(key_mask)
+    p.out, p.out_cols, p.out_ld = out.data_ptr(), out.shape[1], out.stride(0)
+    p.workspace = workspace.data_ptr()
+    p.workspace_bytes = workspace.numel() * workspace.element_size()
+    _check(lib().bdattn_qkvo_fwd(C.byref(p), _stream(stream)))
+
+
+def project_kv(ctx, wk, wv, k_out, v_out, *, bk=None, bv=None, stream=None):
+    """``bdattn_project_kv`` (flash_attention_project_kv)."""
+    _check(lib().bdattn_project_kv(ctx.data_ptr(), ctx.shape[0], ctx.shape[1], ctx.stride(0),
+                                   wk.data_ptr(), _ptr(bk), wv.data_ptr(), _ptr(bv),
+                                   k_out.data_ptr(), v_out.data_ptr(), k_out.stride(0), wk.shape[0],
+                                   _dtype_code(ctx), _stream(stream)))
+
+
+def linear_fwd(x, w, bias, y, *, stream=None):
+    """``bdattn_linear_fwd``: y = x @ w.T + bias."""
+    _check(lib().bdattn_linear_fwd(x.data_ptr(), w.data_ptr(), _ptr(bias), y.data_ptr(),
+                                   _dtype_code(x), x.shape[0], w.shape[0], x.shape[1], x.stride(0),
+                                   w.stride(0), y.stride(0), _stream(stream)))
+
+
+def linear_geglu_fwd(x, w, bias, y, *, stream=None):
+    """``bdattn_linear_geglu_fwd`` (fused_linear_geglu)."""
+    _check(lib().bdattn_linear_geglu_fwd(x.data_ptr(), w.data_ptr(), _ptr(bias), y.data_ptr(),
+                                         _dtype_code(x), x.shape[0], x.shape[1], w.shape[0] // 2,
+                                         _stream(stream)))
+
+
+def add_inplace(y, x, *, stream=None):
+    """``bdattn_add_inplace`` (add_inplace_vec): y += x, both dense."""
+    if y.shape != x.shape or not y.is_contiguous() or not x.is_contiguous():
+        raise BdattnError("add_inplace_vec: Y and X must be dense and of equal shape")
+    _check(lib().bdattn_add_inplace(y.data_ptr(), x.data_ptr(), y.numel(), _dtype_code(y),
+                                    _stream(stream)))
+
+
+def add_row_bias(y, bias, *, stream=None):
+    """``bdattn_add_row_bias`` (add_inplace_row_bias): y[i, j] += bias[j]."""
+    if bias.numel() != y.shape[1]:
+        raise BdattnError("add_inplace_row_bias: bias length must equal the column count")
+    _check(lib().bdattn_add_row_bias(y.data_ptr(), bias.data_ptr(), y.shape[0], y.shape[1],
+                                     y.stride(0), _dtype_code(y), _stream(stream)))

@@ -6,4 +6,6 @@
 #include "norm_rope.cu"
 #include "linear_attn.cu"
 #include "rope_tables.cu"
+#include "gemm_tc05.cu"
+#include "elementwise.cu"
 #include "capi.cu"

@@ -105,6 +105,92 @@ int sdpa_emu_setting() {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// (cols, rows) row-major 16-bit matrix, box = 64 columns x box_rows rows,
+// 128-byte swizzle, zero fill outside.
+int make_map_2d(const char* op, CUtensorMap* m, const void* base, bool bf16, long long cols,
+                long long rows, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail("%s: cuTensorMapEncodeTiled is not available from the driver", op);
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail("%s: cuTensorMapEncodeTiled failed (CUresult %d) for base=%p cols=%lld rows=%lld ld=%lld",
+                    op, static_cast<int>(r), base, cols, rows, ld);
+    return 0;
+}
+
+int round_up(int x, int m) { return (x + m - 1) / m * m; }
+
+// Width each head is padded to for the tensor-core attention kernel (0: the
+// general kernel is used and heads stay unpadded).
+int padded_head_dim(int hd) {
+    if (hd % 8 != 0) return 0;
+    if (hd <= 64) return 64;
+    if (hd <= 128) return 128;
+    return 0;
+}
+
+// One GEMM problem  C[M, N] = A[M, K] . W[N, K]^T (+ bias).  head_dim > 0 cuts
+// the N dimension into per-head tiles whose results land head_pad columns
+// apart (zero filled); head_dim == 0 uses plain 64-column tiles.
+int add_gemm_problem(const char* op, bdattn::GemmLaunch& L, int idx, const void* A, long long lda,
+                     const void* W, long long ldw, const void* bias, void* Cout, long long ldc, int M,
+                     int N, int K, int head_dim, int head_pad, int geglu_offset) {
+    if (A == nullptr || W == nullptr || Cout == nullptr) return fail("%s: null matrix pointer", op);
+    if (M < 1 || N < 1 || K < 1) return fail("%s: empty matrix (M=%d N=%d K=%d)", op, M, N, K);
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ldc % 8 != 0 || lda < K || ldw < K)
+        return fail("%s: inner size and row strides must be multiples of 8 elements (K=%d lda=%lld ldw=%lld "
+                    "ldc=%lld)", op, K, lda, ldw, ldc);
+    if (!aligned16(A) || !aligned16(W) || !aligned16(Cout)) return fail("%s: matrices must be 16-byte aligned", op);
+    bdattn::GemmProblem& p = L.args.p[idx];
+    p.M = M; p.N = N; p.K = K; p.C = Cout; p.ldc = ldc; p.bias = bias;
+    p.tiles_m = (M + 127) / 128;
+    p.geglu_offset = geglu_offset;
+    if (head_dim > 0) {
+        if (N % head_dim != 0) return fail("%s: output width %d is not a multiple of head_dim %d", op, N, head_dim);
+        p.n_tile = round_up(head_dim, 16);
+        p.n_step = head_dim;
+        p.n_valid = head_dim;
+        p.c_step = head_pad;
+        p.c_fill = head_pad;
+        p.tiles_n = N / head_dim;
+    } else {
+        if (N % 8 != 0) return fail("%s: output width must be a multiple of 8 (got %d)", op, N);
+        p.n_tile = 64;
+        p.n_step = 64;
+        p.n_valid = 64;
+        p.c_step = 64;
+        p.c_fill = 64;
+        p.tiles_n = (N + 63) / 64;
+        if (N % 64 != 0) {
+            // last tile is ragged: the epilogue stores only columns below N
+            p.c_fill = 64;
+        }
+    }
+    if (make_map_2d(op, &L.tmA[idx], A, L.bf16, K, M, lda, 128)) return -1;
+    // the weight matrix has N (+ D_out for GEGLU) rows
+    const long long w_rows = geglu_offset > 0 ? static_cast<long long>(N) + geglu_offset : N;
+    if (make_map_2d(op, &L.tmB[idx], W, L.bf16, K, w_rows, ldw, p.n_tile)) return -1;
+    return 0;
+}
+
+void finish_gemm_launch(bdattn::GemmLaunch& L, int n) {
+    L.n_problems = n;
+    for (int i = n; i < 3; ++i) {
+        L.args.p[i] = L.args.p[0];
+        L.args.p[i].tiles_m = 0;
+        L.args.p[i].tiles_n = 0;
+        L.tmA[i] = L.tmA[0];
+        L.tmB[i] = L.tmB[0];
+    }
+}
+
 }  // namespace
 
 extern "C" {
@@ -409,6 +495,215 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     while (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 148 && chunks >= cs * 2) cs *= 2;
     cudaError_t e = bdattn::launch_linear_attn(a, tq, tk, tv, cs, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_linear_fwd(const void* x, const void* w, const void* bias, void* y, int dtype, int M,
+                      int N, int K, long long ldx, long long ldw, long long ldy,
+                      bdattn_stream_t stream) {
+    const char* op = "bdattn_linear_fwd";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: dtype must be BF16 or F16", op);
+    bdattn::GemmLaunch L;
+    std::memset(&L, 0, sizeof(L));
+    L.bf16 = dtype == BDATTN_BF16;
+    if (add_gemm_problem(op, L, 0, x, ldx, w, ldw, bias, y, ldy, M, N, K, 0, 0, 0)) return -1;
+    finish_gemm_launch(L, 1);
+    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_linear_geglu_fwd(const void* x, const void* w, const void* bias, void* y, int dtype,
+                            int rows, int d_in, int d_out, bdattn_stream_t stream) {
+    const char* op = "fused_linear_geglu";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: tensors must be FP16 or BF16", op);
+    bdattn::GemmLaunch L;
+    std::memset(&L, 0, sizeof(L));
+    L.bf16 = dtype == BDATTN_BF16;
+    if (add_gemm_problem(op, L, 0, x, d_in, w, d_in, bias, y, d_out, rows, d_out, d_in, 0, 0, d_out)) return -1;
+    finish_gemm_launch(L, 1);
+    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_add_inplace(void* y, const void* x, long long n, int dtype, bdattn_stream_t stream) {
+    const char* op = "add_inplace_vec";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: tensors must be FP16 or BF16", op);
+    if (y == nullptr || x == nullptr || n < 0) return fail("%s: bad arguments", op);
+    if (n == 0) return 0;
+    cudaError_t e = bdattn::launch_add_inplace(y, x, n, dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_add_row_bias(void* y, const void* bias, int rows, int cols, long long ld, int dtype,
+                        bdattn_stream_t stream) {
+    const char* op = "add_inplace_row_bias";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: tensors must be FP16 or BF16", op);
+    if (y == nullptr || bias == nullptr || rows < 0 || cols < 0 || ld < cols) return fail("%s: bad arguments", op);
+    if (rows == 0 || cols == 0) return 0;
+    cudaError_t e = bdattn::launch_add_row_bias(y, bias, rows, cols, ld, dtype == BDATTN_BF16,
+                                                reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+size_t bdattn_qkvo_workspace_bytes(int q_rows, int kv_rows, int num_heads, int head_dim) {
+    if (q_rows < 0 || kv_rows < 0 || num_heads < 1 || head_dim < 1) return 0;
+    const int pad = padded_head_dim(head_dim) ? padded_head_dim(head_dim) : head_dim;
+    const size_t wq = static_cast<size_t>(q_rows) * num_heads * pad * 2;
+    const size_t wkv = static_cast<size_t>(kv_rows) * num_heads * pad * 2;
+    const size_t wo = static_cast<size_t>(q_rows) * num_heads * head_dim * 2;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    return up(wq) + 2 * up(wkv) + up(wo);
+}
+
+int bdattn_project_kv(const void* ctx, int ctx_rows, int ctx_cols, long long ctx_ld, const void* wk,
+                      const void* bk, const void* wv, const void* bv, void* k_out, void* v_out,
+                      long long kv_ld, int inner_dim, int dtype, bdattn_stream_t stream) {
+    const char* op = "flash_attention_project_kv";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: dtype must be BF16 or F16", op);
+    bdattn::GemmLaunch L;
+    std::memset(&L, 0, sizeof(L));
+    L.bf16 = dtype == BDATTN_BF16;
+    if (add_gemm_problem(op, L, 0, ctx, ctx_ld, wk, ctx_cols, bk, k_out, kv_ld, ctx_rows, inner_dim, ctx_cols, 0, 0, 0)) return -1;
+    if (add_gemm_problem(op, L, 1, ctx, ctx_ld, wv, ctx_cols, bv, v_out, kv_ld, ctx_rows, inner_dim, ctx_cols, 0, 0, 0)) return -1;
+    finish_gemm_launch(L, 2);
+    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
+    if (p == nullptr) return fail("bdattn_qkvo_fwd: params is null");
+    const bool cached = p->k_cached != nullptr || p->v_cached != nullptr;
+    const char* op = cached ? "flash_attention_q_with_kv_cached_forward" : "flash_attention_qkvo_forward";
+    if (require_sm100(op)) return -1;
+    if (p->dtype != BDATTN_BF16 && p->dtype != BDATTN_F16) return fail("%s: dtype must be BF16 or F16", op);
+    const bool bf16 = p->dtype == BDATTN_BF16;
+    if (p->num_heads < 1 || p->inner_dim < 1 || p->inner_dim % p->num_heads != 0)
+        return fail("%s: inner_dim must be a positive multiple of num_heads", op);
+    const int nh = p->num_heads, C = p->inner_dim, hd = C / nh;
+    if (hd % 8 != 0 || hd > 256) return fail("%s: head_dim must be a multiple of 8 up to 256 (got %d)", op, hd);
+    if (p->x == nullptr || p->out == nullptr || p->wq == nullptr || p->wo == nullptr)
+        return fail("%s: x, out, wq and wo must not be null", op);
+    if (p->x_rows < 1) return fail("%s: x has no rows", op);
+    if (cached && (p->k_cached == nullptr || p->v_cached == nullptr || p->kv_rows < 1))
+        return fail("%s: k_cached, v_cached and kv_rows must all be given", op);
+    if (!cached && (p->wk == nullptr || p->wv == nullptr)) return fail("%s: wk and wv must not be null", op);
+    const void* src = p->ctx != nullptr ? p->ctx : p->x;
+    const int src_rows = p->ctx != nullptr ? p->ctx_rows : p->x_rows;
+    const int src_cols = p->ctx != nullptr ? p->ctx_cols : p->x_cols;
+    const long long src_ld = p->ctx != nullptr ? p->ctx_ld : p->x_ld;
+    const int Lq = p->x_rows;
+    const int Lk = cached ? p->kv_rows : src_rows;
+    if (Lk < 1) return fail("%s: no key rows", op);
+    const size_t need = bdattn_qkvo_workspace_bytes(Lq, Lk, nh, hd);
+    if (p->workspace == nullptr || p->workspace_bytes < need)
+        return fail("%s: workspace of %zu bytes needed (got %zu)", op, need, p->workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(p->workspace) & 255u) != 0) return fail("%s: workspace must be 256-byte aligned", op);
+    const int pad = padded_head_dim(hd);
+    const int P = pad ? pad : hd;
+    auto up = [](size_t b) { return (b + 255) / 256 * 256; };
+    uint8_t* ws = static_cast<uint8_t*>(p->workspace);
+    void* Qp = ws;
+    void* Kp = ws + up(static_cast<size_t>(Lq) * nh * P * 2);
+    void* Vp = static_cast<uint8_t*>(Kp) + up(static_cast<size_t>(Lk) * nh * P * 2);
+    void* Op = static_cast<uint8_t*>(Vp) + up(static_cast<size_t>(Lk) * nh * P * 2);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const long long ldp = static_cast<long long>(nh) * P;
+
+    // 1. projections into head-padded Q / K / V
+    {
+        bdattn::GemmLaunch L;
+        std::memset(&L, 0, sizeof(L));
+        L.bf16 = bf16;
+        int n = 0;
+        if (add_gemm_problem(op, L, n++, p->x, p->x_ld, p->wq, p->x_cols, p->bq, Qp, ldp, Lq, C, p->x_cols,
+                             pad ? hd : 0, P, 0)) return -1;
+        if (!cached) {
+            if (add_gemm_problem(op, L, n++, src, src_ld, p->wk, src_cols, p->bk, Kp, ldp, Lk, C, src_cols,
+                                 pad ? hd : 0, P, 0)) return -1;
+            if (add_gemm_problem(op, L, n++, src, src_ld, p->wv, src_cols, p->bv, Vp, ldp, Lk, C, src_cols,
+                                 pad ? hd : 0, P, 0)) return -1;
+        }
+        finish_gemm_launch(L, n);
+        cudaError_t e = bdattn::launch_gemm_tc05(L, st);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+    }
+    const void* Kin = Kp;
+    const void* Vin = Vp;
+    long long k_ld = ldp, v_ld = ldp;
+    if (cached) {
+        if (p->k_ld < C || p->v_ld < C || p->k_ld % 8 || p->v_ld % 8 || !aligned16(p->k_cached) || !aligned16(p->v_cached))
+            return fail("%s: cached K/V must be 16-byte aligned with ld >= inner_dim and a multiple of 8", op);
+        if (P != hd) {
+            cudaError_t e = bdattn::launch_pad_heads(p->k_cached, Kp, Lk, nh, hd, P, p->k_ld, st);
+            if (e == cudaSuccess) e = bdattn::launch_pad_heads(p->v_cached, Vp, Lk, nh, hd, P, p->v_ld, st);
+            if (e != cudaSuccess) return cuda_fail(op, e);
+        } else {
+            Kin = p->k_cached; Vin = p->v_cached; k_ld = p->k_ld; v_ld = p->v_ld;
+        }
+    }
+
+    // 2. attention core
+    const float scale = 1.0f / std::sqrt(static_cast<float>(hd));
+    if (pad) {
+        bdattn::SdpaLaunch L;
+        std::memset(&L, 0, sizeof(L));
+        for (int s = 0; s < 2; ++s) {
+            if (make_map_3d(op, &L.tmQ[s], Qp, bf16, ldp, Lq, 1, ldp, 0, 128)) return -1;
+            if (make_map_3d(op, &L.tmK[s], Kin, bf16, ldp, Lk, 1, k_ld, 0, 128)) return -1;
+            if (make_map_3d(op, &L.tmV[s], Vin, bf16, ldp, Lk, 1, v_ld, 0, 128)) return -1;
+        }
+        bdattn::SdpaDevArgs& a = L.args;
+        a.q_rows[0] = Lq; a.kv_rows[0] = Lk;
+        a.o[0] = Op; a.o_ld[0] = C; a.o_bs[0] = 0;
+        a.q_ctas0 = (Lq + 255) / 256;
+        a.kv_tiles0 = (Lk + 127) / 128;
+        a.kv_tiles = a.kv_tiles0;
+        a.mask_mode = p->causal ? 1 : 0;
+        a.q_offset = Lk - Lq;
+        a.hd_out = hd;
+        a.key_mask = p->key_mask;
+        a.scale_log2 = scale * 1.4426950408889634f;
+        L.q_ctas = a.q_ctas0;
+        L.num_heads = nh; L.batch = 1; L.head_dim = P; L.bf16 = bf16; L.emu = sdpa_emu_setting();
+        cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+    } else {
+        bdattn::SdpaGeneralArgs g;
+        std::memset(&g, 0, sizeof(g));
+        g.q[0] = Qp; g.k[0] = Kin; g.v[0] = Vin; g.o[0] = Op;
+        g.q_rows[0] = Lq; g.kv_rows[0] = Lk;
+        g.q_ld[0] = ldp; g.k_ld[0] = k_ld; g.v_ld[0] = v_ld; g.o_ld[0] = C;
+        g.mask_mode = p->causal ? 1 : 0;
+        g.q_offset = Lk - Lq;
+        g.head_dim = hd;
+        g.key_mask = p->key_mask;
+        g.scale = scale;
+        cudaError_t e = bdattn::launch_sdpa_general(g, nh, 1, bf16, st);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+    }
+
+    // 3. output projection
+    {
+        const int out_cols = p->out_cols > 0 ? p->out_cols : C;
+        bdattn::GemmLaunch L;
+        std::memset(&L, 0, sizeof(L));
+        L.bf16 = bf16;
+        if (add_gemm_problem(op, L, 0, Op, C, p->wo, C, p->bo, p->out, p->out_ld > 0 ? p->out_ld : out_cols, Lq,
+                             out_cols, C, 0, 0, 0)) return -1;
+        finish_gemm_launch(L, 1);
+        cudaError_t e = bdattn::launch_gemm_tc05(L, st);
+        if (e != cudaSuccess) return cuda_fail(op, e);
+    }
     return 0;
 }
 

@@ -138,8 +138,10 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         const long long c0 = static_cast<long long>(tile_n) * p.c_step;
         uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + c0;
         const int n_valid = min(p.n_valid, p.N - n0);
+        // plain tiles stop at the matrix edge; head tiles own their padded slot
+        const int c_lim = p.c_step == p.n_step ? min(p.c_fill, p.N - n0) : p.c_fill;
         if (ok) {
-            for (int c = 0; c < p.c_fill; c += 32) {
+            for (int c = 0; c < c_lim; c += 32) {
                 uint32_t v[32], gt[32];
                 if (c < p.n_tile) {
                     tmem_ld32(tacc + c, v);
@@ -177,7 +179,7 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                 if (row < p.M) {
 #pragma unroll
                     for (int v8 = 0; v8 < 4; ++v8) {
-                        if (c + v8 * 8 < p.c_fill) {
+                        if (c + v8 * 8 < c_lim) {
                             uint4 w;
                             w.x = pack2<kBf16>(f[v8 * 8 + 0], f[v8 * 8 + 1]);
                             w.y = pack2<kBf16>(f[v8 * 8 + 2], f[v8 * 8 + 3]);

@@ -98,6 +98,38 @@ struct LinearAttnArgs {
 cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
                                const CUtensorMap& tmV, int cluster_size, cudaStream_t stream);
 
+// Linear layers (tcgen05 GEMM), up to three problems per launch.
+struct GemmProblem {
+    int M, N, K;
+    void* C;
+    long long ldc;
+    const void* bias;   // N values of the output dtype, or null
+    int tiles_m, tiles_n;
+    int n_tile;         // MMA N (multiple of 16, <= 128) = rows of the B box
+    int n_step;         // weight rows between tile starts
+    int n_valid;        // columns of a tile that carry results
+    int c_step;         // output columns between tile starts
+    int c_fill;         // output columns written per tile (zeros beyond n_valid)
+    int geglu_offset;   // 0, or D_out
+};
+struct GemmArgs {
+    GemmProblem p[3];
+};
+struct GemmLaunch {
+    CUtensorMap tmA[3], tmB[3];
+    GemmArgs args;
+    int n_problems;
+    bool bf16;
+};
+cudaError_t launch_gemm_tc05(const GemmLaunch& L, cudaStream_t stream);
+
+// Elementwise helpers.
+cudaError_t launch_add_inplace(void* y, const void* x, long long n, bool bf16, cudaStream_t stream);
+cudaError_t launch_add_row_bias(void* y, const void* bias, long long rows, long long cols, long long ld,
+                                bool bf16, cudaStream_t stream);
+cudaError_t launch_pad_heads(const void* src, void* dst, int rows, int num_heads, int hd, int hd_pad,
+                             long long src_ld, cudaStream_t stream);
+
 // Device-side RoPE table build.
 constexpr int kMaxRopeSegments = 64;
 struct RopeTableArgs {

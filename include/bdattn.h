@@ -211,6 +211,98 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
                                 const float* sz_in, float w_in, float* sz_out,
                                 bdattn_stream_t stream);
 
+/* -------------------------------------------------- SD1.5 attention block
+ * Fused Q/K/V projection + multi-head attention + output projection.
+ *
+ * bdattn_qkvo_fwd replaces brotensor::flash_attention_qkvo_forward
+ * (src/unet_blocks.cpp:264-271 self-attention, 320-327 cross-attention with
+ * ctx) and, when k_cached / v_cached are given,
+ * brotensor::flash_attention_q_with_kv_cached_forward
+ * (src/unet_blocks.cpp:302-307).  bdattn_project_kv replaces
+ * brotensor::flash_attention_project_kv (src/unet.cpp:476-480), which fills the
+ * per-prompt cross-attention K/V cache.
+ *   x (x_rows, x_cols); ctx (ctx_rows, ctx_cols) or NULL (keys from x);
+ *   wq (inner_dim, x_cols); wk, wv (inner_dim, ctx_cols or x_cols);
+ *   wo (out_cols, inner_dim); biases have one value per output feature, the
+ *   tensor dtype, and may be NULL; out (x_rows, out_cols).
+ * Weights are dense row-major (out_features, in_features).  Heads of 40 or
+ * 80 columns are projected straight into a 64 / 128-wide padded layout in the
+ * workspace so that the attention core runs on the tcgen05 kernel.
+ * The workspace (device memory, 256-byte aligned, size from
+ * bdattn_qkvo_workspace_bytes) holds Q, K, V and the attention output
+ * between the three steps; the call does not allocate.
+ */
+typedef struct bdattn_qkvo_params {
+    int dtype;
+    int num_heads;
+    int inner_dim;          /* num_heads * head_dim */
+    int causal;
+    const void* x;
+    int x_rows;
+    int x_cols;
+    long long x_ld;
+    const void* ctx;        /* NULL: self-attention */
+    int ctx_rows;
+    int ctx_cols;
+    long long ctx_ld;
+    const void* wq;
+    const void* bq;
+    const void* wk;
+    const void* bk;
+    const void* wv;
+    const void* bv;
+    const void* wo;
+    const void* bo;
+    const void* k_cached;   /* (kv_rows, inner_dim) pre-projected keys, or NULL */
+    const void* v_cached;
+    int kv_rows;
+    long long k_ld;
+    long long v_ld;
+    const float* key_mask;  /* Lk floats, 1 = valid; or NULL */
+    void* out;
+    int out_cols;           /* 0 => inner_dim */
+    long long out_ld;       /* 0 => out_cols */
+    void* workspace;
+    size_t workspace_bytes;
+} bdattn_qkvo_params;
+
+size_t bdattn_qkvo_workspace_bytes(int q_rows, int kv_rows, int num_heads, int head_dim);
+
+int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream);
+
+int bdattn_project_kv(const void* ctx, int ctx_rows, int ctx_cols, long long ctx_ld, const void* wk,
+                      const void* bk, const void* wv, const void* bv, void* k_out, void* v_out,
+                      long long kv_ld, int inner_dim, int dtype, bdattn_stream_t stream);
+
+/* ------------------------------------------- linear layer and fused ops
+ * bdattn_linear_fwd: Y(M, N) = X(M, K) W(N, K)^T + bias, the operation behind
+ * the reference's lin_ / linear_batched helpers around attention
+ * (src/dit/flux.cpp:471-484,519-525; include/brodiffusion/detail/compute.h:52-63).
+ *
+ * bdattn_linear_geglu_fwd replaces brodiffusion::fused_linear_geglu
+ * (include/brodiffusion/fused_transformer.h:32-35,
+ * src/fused_transformer.cu:319-358): Y(rows, d_out) = a * gelu_exact(g) with
+ * [a | g] = X W^T + b, W (2*d_out, d_in), b (2*d_out); all tensors dense.
+ *
+ * bdattn_add_inplace replaces brodiffusion::add_inplace_vec
+ * (fused_transformer.h:52, src/fused_transformer.cu:430-451): Y[i] += X[i].
+ *
+ * bdattn_add_row_bias replaces brodiffusion::add_inplace_row_bias
+ * (fused_transformer.h:59-60, src/fused_transformer.cu:413-428):
+ * Y[i, j] += bias[j].
+ */
+int bdattn_linear_fwd(const void* x, const void* w, const void* bias, void* y, int dtype, int M,
+                      int N, int K, long long ldx, long long ldw, long long ldy,
+                      bdattn_stream_t stream);
+
+int bdattn_linear_geglu_fwd(const void* x, const void* w, const void* bias, void* y, int dtype,
+                            int rows, int d_in, int d_out, bdattn_stream_t stream);
+
+int bdattn_add_inplace(void* y, const void* x, long long n, int dtype, bdattn_stream_t stream);
+
+int bdattn_add_row_bias(void* y, const void* bias, int rows, int cols, long long ld, int dtype,
+                        bdattn_stream_t stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
