@@ -117,6 +117,8 @@ def lib():
         L.bdattn_qkvo_workspace_bytes.restype = C.c_size_t
         L.bdattn_qkvo_workspace_bytes.argtypes = [C.c_int] * 4
         L.bdattn_qkvo_fwd.argtypes = [C.POINTER(QkvoParams), C.c_void_p]
+        L.bdattn_qkvo_static_capacity.restype = C.c_size_t
+        L.bdattn_qkvo_fwd_static.argtypes = [C.POINTER(QkvoParams), C.c_void_p]
         L.bdattn_project_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_longlong, C.c_void_p,
                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_longlong, C.c_int, C.c_int, C.c_void_p]
@@ -303,7 +305,10 @@ def qkvo_workspace_bytes(q_rows, kv_rows, num_heads, head_dim) -> int:
 def qkvo_fwd(x, ctx, wq, wk, wv, wo, bo, num_heads, out, workspace, *, bq=None, bk=None, bv=None,
              k_cached=None, v_cached=None, key_mask=None, causal=False, stream=None):
     """``bdattn_qkvo_fwd``: the reference's flash_attention_qkvo_forward, or
-    flash_attention_q_with_kv_cached_forward when k_cached / v_cached are given."""
+    flash_attention_q_with_kv_cached_forward when k_cached / v_cached are given.
+    ``workspace=None`` calls ``bdattn_qkvo_fwd_static`` instead, which keeps its
+    scratch in a fixed array inside the library (for callers that may not
+    allocate device memory; see include/bdattn.h for its limits)."""
     p = QkvoParams()
     p.dtype = _dtype_code(x)
     p.num_heads = num_heads
@@ -319,9 +324,16 @@ def qkvo_fwd(x, ctx, wq, wk, wv, wo, bo, num_heads, out, workspace, *, bq=None, 
         p.kv_rows, p.k_ld, p.v_ld = k_cached.shape[0], k_cached.stride(0), v_cached.stride(0)
     p.key_mask = _ptr(key_mask)
     p.out, p.out_cols, p.out_ld = out.data_ptr(), out.shape[1], out.stride(0)
+    if workspace is None:
+        _check(lib().bdattn_qkvo_fwd_static(C.byref(p), _stream(stream)))
+        return
     p.workspace = workspace.data_ptr()
     p.workspace_bytes = workspace.numel() * workspace.element_size()
     _check(lib().bdattn_qkvo_fwd(C.byref(p), _stream(stream)))
+
+
+def qkvo_static_capacity() -> int:
+    return int(lib().bdattn_qkvo_static_capacity())
 
 
 def project_kv(ctx, wk, wv, k_out, v_out, *, bk=None, bv=None, stream=None):

@@ -9,3 +9,4 @@
 #include "gemm_tc05.cu"
 #include "elementwise.cu"
 #include "capi.cu"
+#include "qkvo_static.cu"

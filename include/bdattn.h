@@ -274,6 +274,33 @@ int bdattn_project_kv(const void* ctx, int ctx_rows, int ctx_cols, long long ctx
                       const void* bk, const void* wv, const void* bv, void* k_out, void* v_out,
                       long long kv_ld, int inner_dim, int dtype, bdattn_stream_t stream);
 
+/* bdattn_qkvo_fwd_static has no counterpart in the reference.  It is
+ * bdattn_qkvo_fwd for callers that are not able to hand over scratch memory
+ * because they may not allocate any: a plugin inside a host application that
+ * has given all device memory to its own pool and forbids cudaMalloc from
+ * plugins, or a latency-critical loop where cudaMalloc / cudaFree are banned
+ * because they synchronise the device.  The scratch is a fixed array inside
+ * the library's device image instead: p->workspace and p->workspace_bytes are
+ * ignored, inputs and outputs are still the caller's.
+ *   - Capacity: bdattn_qkvo_static_capacity() bytes (16 MiB; every SD1.5
+ *     attention call at 512 px fits, the largest needs 14.5 MiB).  A call
+ *     whose bdattn_qkvo_workspace_bytes() exceeds it fails with a message
+ *     that names both sizes.  Every GPU that loads the library keeps these
+ *     16 MiB reserved until the process exits.
+ *   - The call itself makes no cudaMalloc / cudaFree and uses no allocating
+ *     library routine.  The first call on a device looks up the array's device
+ *     address (once per device); make that first call before starting any
+ *     stream capture.
+ *   - All calls on a device share the one array and it keeps what the last
+ *     call left in it.  Nothing in it has to start at zero: each call writes
+ *     every byte it later reads (the projections also write the zero padding
+ *     of the heads).  Two calls whose kernels overlap on the GPU (different
+ *     streams, no ordering between them) race on the array: order them.
+ */
+size_t bdattn_qkvo_static_capacity(void);
+
+int bdattn_qkvo_fwd_static(const bdattn_qkvo_params* p, bdattn_stream_t stream);
+
 /* ------------------------------------------- linear layer and fused ops
  * bdattn_linear_fwd: Y(M, N) = X(M, K) W(N, K)^T + bias, the operation behind
  * the reference's lin_ / linear_batched helpers around attention
