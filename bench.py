@@ -198,9 +198,23 @@ def run_ours(args, rank, world, local_rank):
                           for _ in range(3)))
     qr = torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16)
     kr = torch.empty_like(qr)
+    # N > 1: the head outputs are gathered either by the attention kernel itself
+    # (epilogue stores into every rank's replica through symmetric memory) or,
+    # with --gather nccl, by an in-place NCCL all-gather of a head-major staging tensor.
+    gathered, peer_ptrs, gather_mode = None, None, "none"
+    if world > 1 and args.gather == "fused":
+        try:
+            gathered = headshard.GatheredOutput(batch, L, NH, HD, torch.bfloat16, dev)
+            peer_ptrs = [gathered.peer_ptrs(0), gathered.peer_ptrs(txt)]
+            gather_mode = "fused peer stores in the attention epilogue + symmetric-memory barrier"
+        except Exception as e:      # symmetric memory unavailable: NCCL path
+            gathered = None
+            gather_mode = f"nccl (symmetric memory unavailable: {type(e).__name__})"
+    elif world > 1:
+        gather_mode = "nccl all-gather"
     staging = torch.empty(headshard.staging_shape(world, batch, L, NH, HD), device=dev,
                           dtype=torch.bfloat16)
-    out = staging[rank]
+    out = gathered.local if gathered is not None else staging[rank]
 
     def norm_rope(q, k):
         for b in range(batch):
@@ -213,7 +227,13 @@ def run_ours(args, rank, world, local_rank):
 
     def attention(v):
         bd.sdpa_fwd([qr[:, :txt], qr[:, txt:]], [kr[:, :txt], kr[:, txt:]], [v[:, :txt], v[:, txt:]],
-                    [out[:, :txt], out[:, txt:]], nh_l)
+                    [out[:, :txt], out[:, txt:]], nh_l, peer_out_ptrs=peer_ptrs)
+
+    def gather():
+        if gathered is not None:
+            gathered.barrier()
+        elif world > 1:
+            headshard.all_gather_heads(staging)
 
     launches_per_step = batch + 1
 
@@ -221,8 +241,7 @@ def run_ours(args, rank, world, local_rank):
         q, k, v = sets[i % n_sets]
         norm_rope(q, k)
         attention(v)
-        if world > 1:
-            headshard.all_gather_heads(staging)
+        gather()
 
     def barrier():
         if world > 1:
@@ -292,8 +311,7 @@ def run_ours(args, rank, world, local_rank):
         dv.copy_(hv, non_blocking=True)
         norm_rope(dq, dk)
         attention(dv)
-        if world > 1:
-            headshard.all_gather_heads(staging)
+        gather()
         ho.copy_(out, non_blocking=True)
 
     e2e_steps = max(3, min(args.steps, 10))
@@ -322,7 +340,8 @@ def run_ours(args, rank, world, local_rank):
             "config": {"workload": args.workload, "batch": batch, "tokens": L, "text_tokens": txt,
                        "heads": NH, "head_dim": HD, "heads_per_gpu": nh_l,
                        "step": "rmsnorm+rope (Q,K) -> joint softmax attention" +
-                               (" -> NCCL all-gather of head outputs" if world > 1 else ""),
+                               (" -> all-gather of head outputs" if world > 1 else ""),
+                       "gather": gather_mode,
                        "l2": f"rotating {n_sets} input sets ({n_sets * set_bytes / 1e6:.0f} MB > 126 MB L2)"},
             "clocks": clocks,
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
@@ -378,6 +397,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: how the head outputs are gathered")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -101,6 +101,8 @@ def lib():
         L.bdattn_last_error.restype = C.c_char_p
         L.bdattn_device_status.argtypes = [C.POINTER(C.c_int), C.c_int]
         L.bdattn_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
+        L.bdattn_sdpa_fwd_allgather.argtypes = [C.POINTER(SdpaParams), C.POINTER(C.c_void_p),
+                                                C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
         L.bdattn_rmsnorm_rope.argtypes = [C.POINTER(NormRopeJob), C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_float, C.c_int, C.c_void_p]
         L.bdattn_linear_attn_relu_fwd.argtypes = [
@@ -182,10 +184,12 @@ def device_status(clear: bool = True) -> int:
 
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
-             val_scale=None, softmax_scale=0.0, stream=None):
+             val_scale=None, softmax_scale=0.0, stream=None, peer_out_ptrs=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
-    (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors."""
+    (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
+    ``peer_out_ptrs`` (list per output segment of lists of raw device pointers
+    on other GPUs) selects ``bdattn_sdpa_fwd_allgather``."""
     qs = list(q) if isinstance(q, (list, tuple)) else [q]
     os_ = list(out) if isinstance(out, (list, tuple)) else [out]
     ks = list(k) if isinstance(k, (list, tuple)) else [k]
@@ -220,6 +224,12 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
     p.key_scale = key_scale.data_ptr() if key_scale is not None else None
     p.val_scale = val_scale.data_ptr() if val_scale is not None else None
     p.softmax_scale = softmax_scale
+    if peer_out_ptrs:
+        n = len(peer_out_ptrs[0])
+        a0 = (C.c_void_p * max(n, 1))(*peer_out_ptrs[0])
+        a1 = (C.c_void_p * max(n, 1))(*(peer_out_ptrs[1] if len(peer_out_ptrs) > 1 else [None] * n))
+        _check(lib().bdattn_sdpa_fwd_allgather(C.byref(p), a0, a1, n, _stream(stream)))
+        return
     _check(lib().bdattn_sdpa_fwd(C.byref(p), _stream(stream)))
 
 

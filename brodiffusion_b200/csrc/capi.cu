@@ -103,6 +103,32 @@ int sdpa_emu_setting() {
     return v;
 }
 
+// Attention operand: (head_dim, heads, rows, batch) view of a row-major
+// (rows, heads * head_dim) 16-bit tensor; box = 64 head elements x 1 head x
+// box_rows rows, 128-byte swizzle.  Head elements beyond head_dim read as zero.
+int make_map_heads(const char* op, CUtensorMap* m, const void* base, bool bf16, int head_dim,
+                   int num_heads, long long rows, long long batch, long long ld,
+                   long long batch_stride, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return fail("%s: cuTensorMapEncodeTiled is not available from the driver", op);
+    if (batch_stride <= 0) batch_stride = rows * ld;
+    cuuint64_t dims[4] = {static_cast<cuuint64_t>(head_dim), static_cast<cuuint64_t>(num_heads),
+                          static_cast<cuuint64_t>(rows), static_cast<cuuint64_t>(batch)};
+    cuuint64_t strides[3] = {static_cast<cuuint64_t>(head_dim) * 2, static_cast<cuuint64_t>(ld) * 2,
+                             static_cast<cuuint64_t>(batch_stride) * 2};
+    cuuint32_t box[4] = {64, 1, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                    const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return fail("%s: cuTensorMapEncodeTiled failed (CUresult %d) for base=%p head_dim=%d heads=%d "
+                    "rows=%lld batch=%lld ld=%lld", op, static_cast<int>(r), base, head_dim, num_heads,
+                    rows, batch, ld);
+    return 0;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // (cols, rows) row-major 16-bit matrix, box = 64 columns x box_rows rows,
@@ -216,9 +242,10 @@ int bdattn_device_status(int* status, int clear) {
     return 0;
 }
 
-int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
-    const char* op = "bdattn_sdpa_fwd";
+static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* const* peer_o0,
+                         void* const* peer_o1, int n_peers, bdattn_stream_t stream) {
     if (p == nullptr) return fail("%s: params is null", op);
+    if (n_peers < 0 || n_peers > 8) return fail("%s: n_peers must be in [0, 8]", op);
     if (require_sm100(op)) return -1;
     if (p->dtype != BDATTN_BF16 && p->dtype != BDATTN_F16)
         return fail("%s: dtype must be BF16 or F16 (got %d)", op, p->dtype);
@@ -258,20 +285,23 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
     const bool bf16 = p->dtype == BDATTN_BF16;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
-    if (hd == 64 || hd == 128) {
+    if (hd <= 128) {
+        // tensor-core path: the kernel computes with 64 or 128 columns per head and
+        // the TMA unit zero-pads narrower heads
+        const int hd_kernel = hd <= 64 ? 64 : 128;
         bdattn::SdpaLaunch L;
         std::memset(&L, 0, sizeof(L));
         for (int s = 0; s < 2; ++s) {
             const int qs = s < p->n_q_seg ? s : 0;
             const int ks = s < p->n_kv_seg ? s : 0;
-            if (make_map_3d(op, &L.tmQ[s], p->q[qs], bf16, D, p->q_rows[qs], p->batch, p->q_ld[qs],
-                            p->q_batch_stride[qs], 128))
+            if (make_map_heads(op, &L.tmQ[s], p->q[qs], bf16, hd, p->num_heads, p->q_rows[qs], p->batch,
+                               p->q_ld[qs], p->q_batch_stride[qs], 128))
                 return -1;
-            if (make_map_3d(op, &L.tmK[s], p->k[ks], bf16, D, p->kv_rows[ks], p->batch, p->k_ld[ks],
-                            p->k_batch_stride[ks], 128))
+            if (make_map_heads(op, &L.tmK[s], p->k[ks], bf16, hd, p->num_heads, p->kv_rows[ks], p->batch,
+                               p->k_ld[ks], p->k_batch_stride[ks], 128))
                 return -1;
-            if (make_map_3d(op, &L.tmV[s], p->v[ks], bf16, D, p->kv_rows[ks], p->batch, p->v_ld[ks],
-                            p->v_batch_stride[ks], 128))
+            if (make_map_heads(op, &L.tmV[s], p->v[ks], bf16, hd, p->num_heads, p->kv_rows[ks], p->batch,
+                               p->v_ld[ks], p->v_batch_stride[ks], 128))
                 return -1;
         }
         bdattn::SdpaDevArgs& a = L.args;
@@ -295,10 +325,21 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
         a.key_scale = p->key_scale;
         a.val_scale = p->val_scale;
         a.scale_log2 = scale * 1.4426950408889634f;
+        a.n_peers = n_peers;
+        for (int i = 0; i < n_peers; ++i) {
+            if (peer_o0 == nullptr || peer_o0[i] == nullptr || !aligned16(peer_o0[i]))
+                return fail("%s: peer output %d of segment 0 is null or not 16-byte aligned", op, i);
+            a.o_peer[0][i] = peer_o0[i];
+            if (p->n_q_seg > 1) {
+                if (peer_o1 == nullptr || peer_o1[i] == nullptr || !aligned16(peer_o1[i]))
+                    return fail("%s: peer output %d of segment 1 is null or not 16-byte aligned", op, i);
+                a.o_peer[1][i] = peer_o1[i];
+            }
+        }
         L.q_ctas = a.q_ctas0 + q_ctas1;
         L.num_heads = p->num_heads;
         L.batch = p->batch;
-        L.head_dim = hd;
+        L.head_dim = hd_kernel;
         L.bf16 = bf16;
         L.emu = sdpa_emu_setting();
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
@@ -307,6 +348,7 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
         return 0;
     }
 
+    if (n_peers > 0) return fail("%s: the fused all-gather needs head_dim <= 128", op);
     bdattn::SdpaGeneralArgs g;
     std::memset(&g, 0, sizeof(g));
     for (int s = 0; s < 2; ++s) {
@@ -331,6 +373,15 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
     cudaError_t e = bdattn::launch_sdpa_general(g, p->num_heads, p->batch, bf16, st);
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
+}
+
+int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
+    return sdpa_fwd_impl("bdattn_sdpa_fwd", p, nullptr, nullptr, 0, stream);
+}
+
+int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
+                              int n_peers, bdattn_stream_t stream) {
+    return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, stream);
 }
 
 int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype, int num_heads,
@@ -658,9 +709,9 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
         bdattn::SdpaLaunch L;
         std::memset(&L, 0, sizeof(L));
         for (int s = 0; s < 2; ++s) {
-            if (make_map_3d(op, &L.tmQ[s], Qp, bf16, ldp, Lq, 1, ldp, 0, 128)) return -1;
-            if (make_map_3d(op, &L.tmK[s], Kin, bf16, ldp, Lk, 1, k_ld, 0, 128)) return -1;
-            if (make_map_3d(op, &L.tmV[s], Vin, bf16, ldp, Lk, 1, v_ld, 0, 128)) return -1;
+            if (make_map_heads(op, &L.tmQ[s], Qp, bf16, P, nh, Lq, 1, ldp, 0, 128)) return -1;
+            if (make_map_heads(op, &L.tmK[s], Kin, bf16, P, nh, Lk, 1, k_ld, 0, 128)) return -1;
+            if (make_map_heads(op, &L.tmV[s], Vin, bf16, P, nh, Lk, 1, v_ld, 0, 128)) return -1;
         }
         bdattn::SdpaDevArgs& a = L.args;
         a.q_rows[0] = Lq; a.kv_rows[0] = Lk;

@@ -18,8 +18,9 @@
 //           BF16 high and low parts (two MMAs) so the state keeps ~16 bits,
 //           division by the z row, BF16 store through a staging tile.
 // Tiles arrive by TMA (64-token x 32-row boxes, 128-byte swizzle) into a ring
-// shared by both passes, so the first Q chunks are in flight during the
-// reduction.  HBM-bound: 4 * N * 32 * 2 bytes per (batch, head).
+// shared by both passes and fed by a dedicated producer warp (full / empty
+// mbarriers, no CTA-wide barrier in the loops), so the first Q chunks are in
+// flight during the reduction.  HBM-bound: 4 * N * 32 * 2 bytes per (batch, head).
 #include <cooperative_groups.h>
 
 #include "sdpa_internal.h"
@@ -30,8 +31,8 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kLaThreads = 256;
-constexpr int kLaWarps = 8;
+constexpr int kLaWarps = 8;                   // consumer warps; one more warp feeds the ring by TMA
+constexpr int kLaThreads = (kLaWarps + 1) * 32;
 constexpr int kLaChunk = 128;                 // tokens per ring item
 constexpr int kLaStages = 4;
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
@@ -46,6 +47,7 @@ struct LaSmem {
     float state[48 * 32];   // rows 33..47 zero
     alignas(16) __nv_bfloat16 out_stage[2][32 * kLaOutLd];
     uint64_t full[kLaStages];
+    uint64_t empty[kLaStages];
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -103,39 +105,68 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int c_begin = min(rank * cpc, chunks);
     const int c_end = min(c_begin + cpc, chunks);
     const int n_mine = c_end - c_begin;
-    const int n_items = 2 * n_mine;   // pass A items, then pass B items
+    const int n_items = 2 * n_mine;   // pass A items (K + V chunks), then pass B items (Q chunks)
     const int row0 = head * 32;
 
     if (tid == 0) {
-        for (int s = 0; s < kLaStages; ++s) mbar_init(&sm.full[s], 1);
+        for (int s = 0; s < kLaStages; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], kLaWarps);
+        }
         fence_mbar_init();
     }
     for (int i = tid; i < 48 * 32; i += kLaThreads) sm.state[i] = 0.0f;
     __syncthreads();
 
-    auto issue = [&](int item) {
-        const int slot = item % kLaStages;
-        uint8_t* dst = sm.ring[slot];
-        if (item < n_mine) {
-            const int tok = (c_begin + item) * kLaChunk;
-            mbar_arrive_expect_tx(&sm.full[slot], 4 * kLaBoxBytes);
-            tma_load_3d(dst, &tmK, &sm.full[slot], tok, row0, batch);
-            tma_load_3d(dst + kLaBoxBytes, &tmK, &sm.full[slot], tok + 64, row0, batch);
-            tma_load_3d(dst + 2 * kLaBoxBytes, &tmV, &sm.full[slot], tok, row0, batch);
-            tma_load_3d(dst + 3 * kLaBoxBytes, &tmV, &sm.full[slot], tok + 64, row0, batch);
-        } else {
-            const int tok = (c_begin + item - n_mine) * kLaChunk;
-            mbar_arrive_expect_tx(&sm.full[slot], 2 * kLaBoxBytes);
-            tma_load_3d(dst, &tmQ, &sm.full[slot], tok, row0, batch);
-            tma_load_3d(dst + kLaBoxBytes, &tmQ, &sm.full[slot], tok + 64, row0, batch);
+    if (warp == kLaWarps) {
+        // ------------------------------------------------------- TMA producer
+        bool ok = true;
+        auto issue = [&](int item) {
+            const int slot = item % kLaStages;
+            if (item >= kLaStages) {
+                ok = mbar_wait(&sm.empty[slot], static_cast<uint32_t>(((item / kLaStages) - 1) & 1));
+                if (!ok) return;
+            }
+            uint8_t* dst = sm.ring[slot];
+            if (item < n_mine) {
+                const int tok = (c_begin + item) * kLaChunk;
+                mbar_arrive_expect_tx(&sm.full[slot], 4 * kLaBoxBytes);
+                tma_load_3d(dst, &tmK, &sm.full[slot], tok, row0, batch);
+                tma_load_3d(dst + kLaBoxBytes, &tmK, &sm.full[slot], tok + 64, row0, batch);
+                tma_load_3d(dst + 2 * kLaBoxBytes, &tmV, &sm.full[slot], tok, row0, batch);
+                tma_load_3d(dst + 3 * kLaBoxBytes, &tmV, &sm.full[slot], tok + 64, row0, batch);
+            } else {
+                const int tok = (c_begin + item - n_mine) * kLaChunk;
+                mbar_arrive_expect_tx(&sm.full[slot], 2 * kLaBoxBytes);
+                tma_load_3d(dst, &tmQ, &sm.full[slot], tok, row0, batch);
+                tma_load_3d(dst + kLaBoxBytes, &tmQ, &sm.full[slot], tok + 64, row0, batch);
+            }
+        };
+        // Items whose ring slot is freed during pass A can be issued before the
+        // cluster-wide reduction; the rest follow it (their slots free up in pass B).
+        const int first = min(n_items, n_mine + kLaStages);
+        int issued = 0;
+        if (lane == 0) {
+            for (int it = 0; it < first && ok; ++it) { issue(it); if (ok) issued = it + 1; }
         }
-    };
-    if (tid == 0) {
-        for (int it = 0; it < min(kLaStages, n_items); ++it) issue(it);
+        __syncwarp();
+        cluster.sync();
+        cluster.sync();
+        if (lane == 0) {
+            for (int it = first; it < n_items && ok; ++it) { issue(it); if (ok) issued = it + 1; }
+            if (!ok) {
+                // Unwinding after a wait ran out: let copies in flight land.
+                for (int it = max(0, issued - kLaStages); it < issued; ++it)
+                    mbar_wait(&sm.full[it % kLaStages], static_cast<uint32_t>((it / kLaStages) & 1));
+            }
+        }
+        __syncwarp();
+        cluster.sync();
+        return;
     }
 
+    // ----------------------------------------------------------- consumers
     bool ok = true;
-    // ------------------------------------------------------------- pass A
     float acc[2][4][4];
     float zacc[4];
 #pragma unroll
@@ -149,10 +180,10 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
     const int box = warp >> 2;           // which 64-token box of the chunk
     const int chunk0 = (warp & 3) * 2;   // first 16-byte chunk of this warp's 16 tokens
+    // pass A
     for (int it = 0; it < n_mine; ++it) {
         const int slot = it % kLaStages;
-        ok = mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1));
-        if (!__all_sync(0xffffffffu, ok)) ok = false;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
         if (ok) {
             const uint32_t kb = smem_u32(sm.ring[slot]) + box * kLaBoxBytes;
             const uint32_t vb = kb + 2 * kLaBoxBytes;
@@ -179,12 +210,11 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
         }
-        ok = __syncthreads_and(ok ? 1 : 0) != 0;   // CTA-uniform from here on
-        if (tid == 0 && ok && it + kLaStages < n_items) issue(it + kLaStages);
-        if (!ok) break;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[slot]);   // the operands are in registers
     }
 
-    // ------------------------------------------------------------- reduce
+    // reduce: warps -> CTA (shared memory) -> cluster (distributed shared memory)
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -204,15 +234,15 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         z += __shfl_xor_sync(0xffffffffu, z, 2);
         if (q4 == 0) sm.partial[warp][32 * 32 + nt * 8 + g] = z;
     }
-    __syncthreads();
-    for (int i = tid; i < kLaState; i += kLaThreads) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    for (int i = tid; i < kLaState; i += kLaWarps * 32) {
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < kLaWarps; ++w) s += sm.partial[w][i];
         sm.local_state[i] = s;
     }
     cluster.sync();
-    for (int i = tid; i < kLaState; i += kLaThreads) {
+    for (int i = tid; i < kLaState; i += kLaWarps * 32) {
         float s = 0.0f;
         for (int r = 0; r < cs; ++r) {
             const float* remote = cluster.map_shared_rank(sm.local_state, r);
@@ -225,8 +255,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     cluster.sync();
 
-    // ------------------------------------------------------------- pass B
-    // A fragments of [S; z] (48 x 32, rows 33.. zero), split hi + lo.
+    // pass B: A fragments of [S; z] (48 x 32, rows 33.. zero), split hi + lo
     uint32_t ah[3][2][4], al[3][2][4];
 #pragma unroll
     for (int mt = 0; mt < 3; ++mt)
@@ -244,10 +273,9 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 al[mt][ks][r] = pack2<true>(x0 - h0, x1 - h1);
             }
 
-    for (int it = n_mine; ok && it < n_items; ++it) {
+    for (int it = n_mine; it < n_items; ++it) {
         const int slot = it % kLaStages;
-        ok = mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1));
-        if (!__all_sync(0xffffffffu, ok)) ok = false;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
         const int cidx = it - n_mine;
         __nv_bfloat16* stage = sm.out_stage[cidx & 1];
         if (ok) {
@@ -287,13 +315,14 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
         }
-        ok = __syncthreads_and(ok ? 1 : 0) != 0;
-        if (tid == 0 && ok && it + kLaStages < n_items) issue(it + kLaStages);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.empty[slot]);
+        asm volatile("bar.sync 1, 256;" ::: "memory");   // the 32 x 128 output tile is complete
         if (ok) {
             const int tok0 = (c_begin + cidx) * kLaChunk;
 #pragma unroll
             for (int rep = 0; rep < 2; ++rep) {
-                const int idx = tid + rep * kLaThreads;
+                const int idx = tid + rep * kLaWarps * 32;
                 const int row = idx >> 4;
                 const int c16 = idx & 15;
                 const int tok = tok0 + c16 * 8;
@@ -306,10 +335,6 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 }
             }
         }
-    }
-    if (!ok && tid == 0) {
-        // Unwinding after a wait ran out: let copies in flight land.
-        for (int s = 0; s < kLaStages; ++s) mbar_wait(&sm.full[s], 0);
     }
     cluster.sync();
 }

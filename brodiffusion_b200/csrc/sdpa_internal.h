@@ -23,6 +23,10 @@ struct SdpaDevArgs {
     const float* key_scale;
     const float* val_scale;
     float scale_log2;  // softmax scale * log2(e)
+    // Fused all-gather: every output vector is also stored to the same offset of
+    // these peer buffers (other GPUs' copies of the output tensor), per segment.
+    int n_peers;
+    void* o_peer[2][8];
 };
 
 struct SdpaLaunch {

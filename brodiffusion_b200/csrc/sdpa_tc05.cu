@@ -27,6 +27,11 @@
 // on the FMA pipe with a degree-3 polynomial instead of ex2.approx (relative
 // error 1.0e-4, below the 2^-9 rounding of P to BF16).
 //
+// Q, K and V are addressed through 4-D tensor maps (head element, head, row,
+// batch): a head narrower than the 64 / 128 columns the kernel computes with
+// (40, 72, 80, 112, ...) is zero-padded by the TMA unit itself, so such head
+// dims run here without a padding pass; only the real columns are stored.
+//
 // Arithmetic follows the attention core of dit::joint_attention_traced
 // (src/dit/common.cpp:246-305): scale 1/sqrt(hd), stable softmax,
 // inv = denom > 0 ? 1/denom : 0, with FP32 scores and accumulation.
@@ -356,11 +361,12 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         const float inv = (l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
         const bool row_ok = ok && row_in_seg < seg_rows;
         uint8_t* orow = nullptr;
+        long long ooff = 0;      // byte offset of this row's head slice inside the output tensor
         if (row_ok) {
-            orow = reinterpret_cast<uint8_t*>(qseg ? a.o[1] : a.o[0]) +
-                   2 * (static_cast<long long>(batch) * (qseg ? a.o_bs[1] : a.o_bs[0]) +
+            ooff = 2 * (static_cast<long long>(batch) * (qseg ? a.o_bs[1] : a.o_bs[0]) +
                         static_cast<long long>(row_in_seg) * (qseg ? a.o_ld[1] : a.o_ld[0]) +
                         static_cast<long long>(head) * a.hd_out);
+            orow = reinterpret_cast<uint8_t*>(qseg ? a.o[1] : a.o[0]) + ooff;
         }
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
@@ -382,6 +388,12 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                         w.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
                         w.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
                         *reinterpret_cast<uint4*>(orow + (c * 32 + g * 8) * 2) = w;
+                        // fused all-gather: the same vector goes to every peer's copy of
+                        // the output (plain stores over NVLink, no TMA, no multicast)
+                        for (int pi = 0; pi < a.n_peers; ++pi) {
+                            uint8_t* pb = reinterpret_cast<uint8_t*>(qseg ? a.o_peer[1][pi] : a.o_peer[0][pi]);
+                            *reinterpret_cast<uint4*>(pb + ooff + (c * 32 + g * 8) * 2) = w;
+                        }
                     }
                 }
             }
@@ -466,8 +478,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 for (int t = 0; t < 2; ++t) {
                     mbar_arrive_expect_tx(&q_full[t], C::kQBytes);
                     for (int c = 0; c < C::kChunks; ++c) {
-                        tma_load_3d(smem_q + t * C::kQBytes + c * kChunkBytes, mq, &q_full[t],
-                                    head * HD + c * 64, qrow0 + t * kBM, batch);
+                        tma_load_4d(smem_q + t * C::kQBytes + c * kChunkBytes, mq, &q_full[t],
+                                    c * 64, head, qrow0 + t * kBM, batch);
                     }
                 }
                 int issued = 0;
@@ -482,8 +494,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     const CUtensorMap* m = (i & 1) ? (ti.seg ? &tmV1 : &tmV0) : (ti.seg ? &tmK1 : &tmK0);
                     mbar_arrive_expect_tx(&kv_full[slot], C::kTileBytes);
                     for (int c = 0; c < C::kChunks; ++c) {
-                        tma_load_3d(smem_kv + slot * C::kTileBytes + c * kChunkBytes, m, &kv_full[slot],
-                                    head * HD + c * 64, ti.row0, batch);
+                        tma_load_4d(smem_kv + slot * C::kTileBytes + c * kChunkBytes, m, &kv_full[slot],
+                                    c * 64, head, ti.row0, batch);
                     }
                     issued = i + 1;
                 }
@@ -501,6 +513,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
     }
 
+    if (a.n_peers > 0) __threadfence_system();   // peer stores are performed before the kernel retires
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {

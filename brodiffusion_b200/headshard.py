@@ -61,3 +61,40 @@ def project_staged(staging, w_out, bias=None):
     if bias is not None:
         y = y + bias
     return y
+
+
+class GatheredOutput:
+    """Full (B, L, D) attention output replicated on every rank in symmetric
+    memory, for the fused all-gather (``bdattn_sdpa_fwd_allgather``): each rank's
+    attention kernel stores its head columns into every replica through
+    peer-mapped pointers, so after ``barrier()`` every rank holds the reference
+    layout (B, L, num_heads * head_dim) without a staging copy or an NCCL call.
+    """
+
+    def __init__(self, batch, rows, num_heads, head_dim, dtype, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.h0, self.h1 = head_range(num_heads, self.world, self.rank)
+        self.head_dim = head_dim
+        self.full = symm_mem.empty((batch, rows, num_heads * head_dim), dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.full, self.group)
+        self.col0 = self.h0 * head_dim
+        self.elem = self.full.element_size()
+        # this rank's head columns inside its own replica
+        self.local = self.full[:, :, self.col0:self.h1 * head_dim]
+        self.peer_bases = [int(self.handle.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+
+    def peer_ptrs(self, row0=0):
+        """Peer addresses of element (0, row0, first own column)."""
+        D = self.full.shape[2]
+        off = (row0 * D + self.col0) * self.elem
+        return [b + off for b in self.peer_bases]
+
+    def barrier(self):
+        """Stream-ordered cross-GPU barrier: once it has passed on this rank's
+        stream, every rank's attention kernel enqueued before its own barrier
+        has completed, so all head columns of the local replica are written."""
+        self.handle.barrier()

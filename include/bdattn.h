@@ -121,6 +121,22 @@ typedef struct bdattn_sdpa_params {
 
 int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
 
+/* Head-sharded attention with the all-gather of head outputs fused into the
+ * kernel (no counterpart in the reference, which is single-device).  Rank g
+ * of G computes its heads and p->o[] is ITS copy of the full (L, D) output,
+ * offset to its own head columns (o_ld = D).  peer_o0[i] (and peer_o1[i] for
+ * the second query segment) are the same location inside the copies that live
+ * on the other GPUs, as pointers this process can store through (peer-mapped /
+ * symmetric memory).  The epilogue writes every output vector to the local
+ * copy and to all n_peers (<= 8) peer copies with plain 16-byte stores over
+ * NVLink, so the transfer overlaps the attention of later tiles and no
+ * staging or NCCL call is needed; the kernel uses no TMA multicast and never
+ * reads peer memory.  The caller orders the consumers: a cross-GPU barrier
+ * after the call (all ranks' kernels complete) before any rank reads the
+ * gathered tensor.  head_dim 64 or 128 only. */
+int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
+                              int n_peers, bdattn_stream_t stream);
+
 /* ------------------------------------------------- per-head RMSNorm + RoPE
  * out = rope(rms_norm_heads(x) * gain).  Replaces the headnorm view +
  * brotensor::rms_norm_forward (src/dit/flux.cpp:462-469,

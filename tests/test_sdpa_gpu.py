@@ -236,8 +236,23 @@ def test_flux_2048_batch2_shape_properties(bd, oracle):
     G.check(G.host(out[1])[rows], ref, what="flux2048 batch item 1")
 
 
+def test_sana_and_pixart_cross_attention_head_dims(bd, oracle):
+    """Head dims 72 (Sana 0.6B / PixArt cross-attention, src/dit/sana.cpp:599-631,
+    src/dit/pixart.cpp:359-365) and 112 (Sana 1.6B) run on the tensor-core kernel
+    with the head zero-padded by the TMA unit; 300 caption keys with a key mask."""
+    for nh, hd in ((16, 72), (20, 112)):
+        Lq, Lk = 1024, 300
+        q = synth.activations((Lq, nh * hd), 9000 + hd)
+        k = synth.activations((Lk, nh * hd), 9001 + hd)
+        v = synth.activations((Lk, nh * hd), 9002 + hd)
+        km = np.ones(Lk, np.float32); km[200:] = 0.0
+        rows = G.boundary_rows(Lq, extra=8)
+        out = G.sdpa(bd, q, k, v, nh, key_mask=km)
+        G.check(out[rows], oracle.sdpa(q, k, v, nh, key_mask=km, rows=rows), what=f"hd={hd} masked cross-attn")
+
+
 # --------------------------------------------------------------- edge cases
-@pytest.mark.parametrize("hd", [128, 64, 40])
+@pytest.mark.parametrize("hd", [128, 64, 40, 72, 112, 160])
 @pytest.mark.parametrize("L", [1, 63, 64, 65, 127, 129, 257])
 def test_ragged_lengths(bd, oracle, L, hd):
     nh = 2
