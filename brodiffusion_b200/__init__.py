@@ -64,6 +64,17 @@ class RopeSegment(C.Structure):
     _fields_ = [("kind", C.c_int), ("n_tokens", C.c_int), ("h", C.c_int), ("w", C.c_int)]
 
 
+class TraceParams(C.Structure):
+    """Mirror of ``bdattn_trace_params`` (include/bdattn.h)."""
+    _fields_ = [
+        ("bias", C.c_void_p), ("bias_row0", C.c_int), ("bias_rows", C.c_int), ("bias_cols", C.c_int),
+        ("bias_ld", C.c_longlong),
+        ("attn_avg", C.c_void_p), ("map_row0", C.c_int), ("map_rows", C.c_int), ("map_cols", C.c_int),
+        ("map_ld", C.c_longlong),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+    ]
+
+
 class QkvoParams(C.Structure):
     """Mirror of ``bdattn_qkvo_params`` (include/bdattn.h)."""
     _fields_ = [
@@ -103,6 +114,9 @@ def lib():
         L.bdattn_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
         L.bdattn_sdpa_fwd_allgather.argtypes = [C.POINTER(SdpaParams), C.POINTER(C.c_void_p),
                                                 C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+        L.bdattn_sdpa_traced_workspace_bytes.restype = C.c_size_t
+        L.bdattn_sdpa_traced_workspace_bytes.argtypes = [C.c_int, C.c_int]
+        L.bdattn_sdpa_traced_fwd.argtypes = [C.POINTER(SdpaParams), C.POINTER(TraceParams), C.c_void_p]
         L.bdattn_rmsnorm_rope.argtypes = [C.POINTER(NormRopeJob), C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_float, C.c_int, C.c_void_p]
         L.bdattn_linear_attn_relu_fwd.argtypes = [
@@ -184,7 +198,7 @@ def device_status(clear: bool = True) -> int:
 
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
-             val_scale=None, softmax_scale=0.0, stream=None, peer_out_ptrs=None):
+             val_scale=None, softmax_scale=0.0, stream=None, peer_out_ptrs=None, _trace=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
     (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
@@ -224,6 +238,9 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
     p.key_scale = key_scale.data_ptr() if key_scale is not None else None
     p.val_scale = val_scale.data_ptr() if val_scale is not None else None
     p.softmax_scale = softmax_scale
+    if _trace is not None:
+        _check(lib().bdattn_sdpa_traced_fwd(C.byref(p), C.byref(_trace), _stream(stream)))
+        return
     if peer_out_ptrs:
         n = len(peer_out_ptrs[0])
         a0 = (C.c_void_p * max(n, 1))(*peer_out_ptrs[0])
@@ -382,3 +399,27 @@ def add_row_bias(y, bias, *, stream=None):
         raise BdattnError("add_inplace_row_bias: bias length must equal the column count")
     _check(lib().bdattn_add_row_bias(y.data_ptr(), bias.data_ptr(), y.shape[0], y.shape[1],
                                      y.stride(0), _dtype_code(y), _stream(stream)))
+
+
+def sdpa_traced_fwd(q, k, v, out, num_heads, *, bias=None, bias_row0=0, map_row0=0, map_rows=0,
+                    map_cols=0, mask_mode=MASK_NONE, key_mask=None, stream=None):
+    """``bdattn_sdpa_traced_fwd``: attention with an optional FP32 logit bias on
+    queries [bias_row0, bias_row0 + bias.shape[0]) x keys [0, bias.shape[1]) and,
+    when map_rows > 0, the head-averaged softmax block (map_rows, map_cols)
+    returned as an FP32 tensor."""
+    import torch
+    qs = list(q) if isinstance(q, (list, tuple)) else [q]
+    Lq = sum(t.shape[-2] for t in qs)
+    t = TraceParams()
+    if bias is not None:
+        t.bias, t.bias_row0 = bias.data_ptr(), bias_row0
+        t.bias_rows, t.bias_cols, t.bias_ld = bias.shape[0], bias.shape[1], bias.stride(0)
+    amap = None
+    if map_rows > 0:
+        amap = torch.empty(map_rows, map_cols, device=qs[0].device, dtype=torch.float32)
+        t.attn_avg, t.map_row0, t.map_rows, t.map_cols, t.map_ld = amap.data_ptr(), map_row0, map_rows, map_cols, map_cols
+    ws = torch.empty(int(lib().bdattn_sdpa_traced_workspace_bytes(num_heads, Lq)), device=qs[0].device,
+                     dtype=torch.uint8)
+    t.workspace, t.workspace_bytes = ws.data_ptr(), ws.numel()
+    sdpa_fwd(q, k, v, out, num_heads, mask_mode=mask_mode, key_mask=key_mask, stream=stream, _trace=t)
+    return amap

@@ -8,5 +8,6 @@
 #include "rope_tables.cu"
 #include "gemm_tc05.cu"
 #include "elementwise.cu"
+#include "attn_map.cu"
 #include "capi.cu"
 #include "qkvo_static.cu"

@@ -243,7 +243,8 @@ int bdattn_device_status(int* status, int clear) {
 }
 
 static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* const* peer_o0,
-                         void* const* peer_o1, int n_peers, bdattn_stream_t stream) {
+                         void* const* peer_o1, int n_peers, const bdattn_trace_params* tr,
+                         bdattn_stream_t stream) {
     if (p == nullptr) return fail("%s: params is null", op);
     if (n_peers < 0 || n_peers > 8) return fail("%s: n_peers must be in [0, 8]", op);
     if (require_sm100(op)) return -1;
@@ -325,6 +326,14 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         a.key_scale = p->key_scale;
         a.val_scale = p->val_scale;
         a.scale_log2 = scale * 1.4426950408889634f;
+        if (tr != nullptr) {
+            a.bias = tr->bias;
+            a.bias_row0 = tr->bias_row0; a.bias_rows = tr->bias_rows; a.bias_cols = tr->bias_cols;
+            a.bias_ld = tr->bias_ld > 0 ? tr->bias_ld : tr->bias_cols;
+            a.bias_mul = 1.0f / scale;
+            a.lse = static_cast<float*>(tr->workspace);
+            a.lq_total = static_cast<int>(Lq);
+        }
         a.n_peers = n_peers;
         for (int i = 0; i < n_peers; ++i) {
             if (peer_o0 == nullptr || peer_o0[i] == nullptr || !aligned16(peer_o0[i]))
@@ -349,6 +358,7 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
     }
 
     if (n_peers > 0) return fail("%s: the fused all-gather needs head_dim <= 128", op);
+    if (tr != nullptr) return fail("%s: traced attention needs head_dim <= 128", op);
     bdattn::SdpaGeneralArgs g;
     std::memset(&g, 0, sizeof(g));
     for (int s = 0; s < 2; ++s) {
@@ -376,12 +386,64 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
 }
 
 int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
-    return sdpa_fwd_impl("bdattn_sdpa_fwd", p, nullptr, nullptr, 0, stream);
+    return sdpa_fwd_impl("bdattn_sdpa_fwd", p, nullptr, nullptr, 0, nullptr, stream);
 }
 
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream) {
-    return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, stream);
+    return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, nullptr, stream);
+}
+
+size_t bdattn_sdpa_traced_workspace_bytes(int num_heads, int q_rows_total) {
+    if (num_heads < 1 || q_rows_total < 1) return 0;
+    return static_cast<size_t>(num_heads) * q_rows_total * 2 * sizeof(float);
+}
+
+int bdattn_sdpa_traced_fwd(const bdattn_sdpa_params* p, const bdattn_trace_params* t,
+                           bdattn_stream_t stream) {
+    const char* op = "joint_attention_traced";
+    if (p == nullptr || t == nullptr) return fail("%s: params is null", op);
+    if (p->batch != 1) return fail("%s: batch must be 1", op);
+    long long Lq = 0, Lk = 0;
+    for (int s = 0; s < p->n_q_seg && s < 2; ++s) Lq += p->q_rows[s];
+    for (int s = 0; s < p->n_kv_seg && s < 2; ++s) Lk += p->kv_rows[s];
+    if (t->bias != nullptr) {
+        if (t->bias_rows < 1 || t->bias_cols < 1 || t->bias_row0 < 0 || t->bias_row0 + t->bias_rows > Lq ||
+            t->bias_cols > Lk)
+            return fail("%s: bias block (rows %d..%d, %d cols) does not fit the %lld x %lld score matrix", op,
+                        t->bias_row0, t->bias_row0 + t->bias_rows, t->bias_cols, Lq, Lk);
+    }
+    if (t->attn_avg != nullptr) {
+        if (t->map_rows < 1 || t->map_cols < 1 || t->map_row0 < 0 || t->map_row0 + t->map_rows > Lq ||
+            t->map_cols > Lk)
+            return fail("%s: map block (rows %d..%d, %d cols) does not fit the %lld x %lld score matrix", op,
+                        t->map_row0, t->map_row0 + t->map_rows, t->map_cols, Lq, Lk);
+    }
+    const size_t need = bdattn_sdpa_traced_workspace_bytes(p->num_heads, static_cast<int>(Lq));
+    if (t->workspace == nullptr || t->workspace_bytes < need)
+        return fail("%s: workspace of %zu bytes needed (got %zu)", op, need, t->workspace_bytes);
+    if (sdpa_fwd_impl(op, p, nullptr, nullptr, 0, t, stream)) return -1;
+    if (t->attn_avg == nullptr) return 0;
+    const int hd = p->head_dim;
+    bdattn::AttnMapArgs m;
+    std::memset(&m, 0, sizeof(m));
+    for (int s = 0; s < 2; ++s) {
+        if (s < p->n_q_seg) { m.q[s] = p->q[s]; m.q_rows[s] = p->q_rows[s]; m.q_ld[s] = p->q_ld[s]; }
+        if (s < p->n_kv_seg) { m.k[s] = p->k[s]; m.kv_rows[s] = p->kv_rows[s]; m.k_ld[s] = p->k_ld[s]; }
+    }
+    if (p->n_q_seg == 1) m.q_rows[0] = static_cast<int>(Lq);
+    if (p->n_kv_seg == 1) m.kv_rows[0] = static_cast<int>(Lk);
+    m.num_heads = p->num_heads; m.head_dim = hd;
+    const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(hd));
+    m.scale_log2 = scale * 1.4426950408889634f;
+    m.lse = static_cast<const float*>(t->workspace); m.lq_total = static_cast<int>(Lq);
+    m.bias = t->bias; m.bias_row0 = t->bias_row0; m.bias_rows = t->bias_rows; m.bias_cols = t->bias_cols;
+    m.bias_ld = t->bias_ld > 0 ? t->bias_ld : t->bias_cols;
+    m.map = t->attn_avg; m.map_row0 = t->map_row0; m.map_rows = t->map_rows; m.map_cols = t->map_cols;
+    m.map_ld = t->map_ld > 0 ? t->map_ld : t->map_cols;
+    cudaError_t e = bdattn::launch_attn_map(m, p->dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
 }
 
 int bdattn_rmsnorm_rope(const bdattn_norm_rope_job* jobs, int n_jobs, int dtype, int num_heads,

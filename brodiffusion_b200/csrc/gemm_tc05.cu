@@ -25,11 +25,15 @@ namespace bdattn {
 namespace {
 
 constexpr int kGemmThreads = 192;
-constexpr int kGemmStages = 4;
+constexpr int kGemmMaxStages = 4;
 constexpr int kGemmABytes = 128 * 64 * 2;   // A stage
-constexpr int kGemmBBytes = 128 * 64 * 2;   // B stage (n_tile <= 128)
-constexpr int kGemmStageBytes = kGemmABytes + 2 * kGemmBBytes;   // + gate tile
-constexpr int kGemmSmemBytes = kGemmStages * kGemmStageBytes + 256 + 1024;
+// A B (or gate) tile is n_tile rows x 128 B; a stage holds A, B and, for GEGLU,
+// the gate tile, rounded up to the 1024-byte swizzle period.  Sizing the stage by
+// the tile shape keeps a 64-column GEMM at 96 KB so that two CTAs share an SM.
+__host__ __device__ inline int gemm_b_bytes(int n_tile) { return (n_tile * 128 + 1023) / 1024 * 1024; }
+__host__ __device__ inline int gemm_stage_bytes(int n_tile, bool geglu) {
+    return kGemmABytes + (geglu ? 2 : 1) * gemm_b_bytes(n_tile);
+}
 
 template <bool kBf16>
 __global__ void __launch_bounds__(kGemmThreads)
@@ -48,10 +52,13 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
     extern __shared__ uint8_t gemm_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
+    const int kGemmStages = g.stages;
+    const int kGemmBBytes = gemm_b_bytes(g.n_tile_max);
+    const int kGemmStageBytes = gemm_stage_bytes(g.n_tile_max, g.any_geglu != 0);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kGemmStages * kGemmStageBytes);
     uint64_t* full = bars;
-    uint64_t* empty = bars + kGemmStages;
-    uint64_t* acc_done = empty + kGemmStages;
+    uint64_t* empty = bars + kGemmMaxStages;
+    uint64_t* acc_done = empty + kGemmMaxStages;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -204,23 +211,31 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
 }  // namespace
 
 cudaError_t launch_gemm_tc05(const GemmLaunch& L, cudaStream_t stream) {
-    int tn = 0, tm = 0;
+    int tn = 0, tm = 0, nt_max = 16, any_geglu = 0;
     for (int i = 0; i < L.n_problems; ++i) {
         tn = L.args.p[i].tiles_n > tn ? L.args.p[i].tiles_n : tn;
         tm = L.args.p[i].tiles_m > tm ? L.args.p[i].tiles_m : tm;
+        nt_max = L.args.p[i].n_tile > nt_max ? L.args.p[i].n_tile : nt_max;
+        any_geglu |= L.args.p[i].geglu_offset > 0 ? 1 : 0;
     }
+    GemmArgs args = L.args;
+    args.n_tile_max = nt_max;
+    args.any_geglu = any_geglu;
+    // three stages with the gate tile: the stage ring stays below 114 KB and two CTAs fit per SM
+    args.stages = any_geglu ? 3 : kGemmMaxStages;
+    const int kGemmSmemBytes = args.stages * gemm_stage_bytes(nt_max, any_geglu != 0) + 256 + 1024;
     dim3 grid(static_cast<unsigned>(tn), static_cast<unsigned>(tm), static_cast<unsigned>(L.n_problems));
     cudaError_t e;
     if (L.bf16) {
-        e = cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         gemm_tc05_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
-            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], L.args);
+            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], args);
     } else {
-        e = cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes);
+        e = cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         gemm_tc05_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
-            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], L.args);
+            L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], args);
     }
     return cudaGetLastError();
 }

@@ -34,7 +34,7 @@ namespace cg = cooperative_groups;
 constexpr int kLaWarps = 8;                   // consumer warps; one more warp feeds the ring by TMA
 constexpr int kLaThreads = (kLaWarps + 1) * 32;
 constexpr int kLaChunk = 128;                 // tokens per ring item
-constexpr int kLaStages = 4;
+constexpr int kLaStages = 8;                  // 8 x 16 KB in flight per SM
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
 constexpr int kLaState = 33 * 32;             // [S; z] floats
@@ -105,7 +105,8 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int c_begin = min(rank * cpc, chunks);
     const int c_end = min(c_begin + cpc, chunks);
     const int n_mine = c_end - c_begin;
-    const int n_items = 2 * n_mine;   // pass A items (K + V chunks), then pass B items (Q chunks)
+    const int n_b = (n_mine + 1) / 2;  // pass B items carry two 128-token Q chunks (16 KB, like a pass A item)
+    const int n_items = n_mine + n_b;  // pass A items (K + V chunks), then pass B items
     const int row0 = head * 32;
 
     if (tid == 0) {
@@ -136,10 +137,11 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 tma_load_3d(dst + 2 * kLaBoxBytes, &tmV, &sm.full[slot], tok, row0, batch);
                 tma_load_3d(dst + 3 * kLaBoxBytes, &tmV, &sm.full[slot], tok + 64, row0, batch);
             } else {
-                const int tok = (c_begin + item - n_mine) * kLaChunk;
-                mbar_arrive_expect_tx(&sm.full[slot], 2 * kLaBoxBytes);
-                tma_load_3d(dst, &tmQ, &sm.full[slot], tok, row0, batch);
-                tma_load_3d(dst + kLaBoxBytes, &tmQ, &sm.full[slot], tok + 64, row0, batch);
+                const int tok = (c_begin + 2 * (item - n_mine)) * kLaChunk;
+                mbar_arrive_expect_tx(&sm.full[slot], 4 * kLaBoxBytes);
+#pragma unroll
+                for (int bx = 0; bx < 4; ++bx)
+                    tma_load_3d(dst + bx * kLaBoxBytes, &tmQ, &sm.full[slot], tok + 64 * bx, row0, batch);
             }
         };
         // Items whose ring slot is freed during pass A can be issued before the
@@ -276,65 +278,69 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int it = n_mine; it < n_items; ++it) {
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
-        const int cidx = it - n_mine;
-        __nv_bfloat16* stage = sm.out_stage[cidx & 1];
-        if (ok) {
-            const uint32_t qb = smem_u32(sm.ring[slot]) + box * kLaBoxBytes;
+#pragma unroll 1
+        for (int sub = 0; sub < 2; ++sub) {
+            const int cidx = 2 * (it - n_mine) + sub;     // 128-token chunk of this CTA
+            if (cidx >= n_mine) break;
+            __nv_bfloat16* stage = sm.out_stage[cidx & 1];
+            if (ok) {
+                const uint32_t qb = smem_u32(sm.ring[slot]) + (2 * sub + box) * kLaBoxBytes;
 #pragma unroll
-            for (int nt = 0; nt < 2; ++nt) {
-                uint32_t b[4];
-                ldsm_x4_trans(qb + swz(lane, chunk0 + nt), b[0], b[1], b[2], b[3]);
+                for (int nt = 0; nt < 2; ++nt) {
+                    uint32_t b[4];
+                    ldsm_x4_trans(qb + swz(lane, chunk0 + nt), b[0], b[1], b[2], b[3]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
-                float o[3][4];
+                    for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
+                    float o[3][4];
 #pragma unroll
-                for (int mt = 0; mt < 3; ++mt) {
+                    for (int mt = 0; mt < 3; ++mt) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) o[mt][i] = 0.0f;
+                        for (int i = 0; i < 4; ++i) o[mt][i] = 0.0f;
 #pragma unroll
-                    for (int ks = 0; ks < 2; ++ks) {
-                        mma_bf16(o[mt], ah[mt][ks][0], ah[mt][ks][1], ah[mt][ks][2], ah[mt][ks][3],
-                                 b[2 * ks], b[2 * ks + 1]);
-                        mma_bf16(o[mt], al[mt][ks][0], al[mt][ks][1], al[mt][ks][2], al[mt][ks][3],
-                                 b[2 * ks], b[2 * ks + 1]);
+                        for (int ks = 0; ks < 2; ++ks) {
+                            mma_bf16(o[mt], ah[mt][ks][0], ah[mt][ks][1], ah[mt][ks][2], ah[mt][ks][3],
+                                     b[2 * ks], b[2 * ks + 1]);
+                            mma_bf16(o[mt], al[mt][ks][0], al[mt][ks][1], al[mt][ks][2], al[mt][ks][3],
+                                     b[2 * ks], b[2 * ks + 1]);
+                        }
+                    }
+                    // Row 32 (z . relu(q)) sits in row 0 of the third tile: lanes 0..3.
+                    const float den0 = __shfl_sync(0xffffffffu, o[2][0], q4);
+                    const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
+                    const float r0 = 1.0f / (den0 + a.eps);
+                    const float r1 = 1.0f / (den1 + a.eps);
+                    const int tok = warp * 16 + nt * 8 + q4 * 2;
+#pragma unroll
+                    for (int mt = 0; mt < 2; ++mt) {
+                        const int i0 = mt * 16 + g;
+                        *reinterpret_cast<uint32_t*>(&stage[i0 * kLaOutLd + tok]) =
+                            pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
+                        *reinterpret_cast<uint32_t*>(&stage[(i0 + 8) * kLaOutLd + tok]) =
+                            pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
                     }
                 }
-                // Row 32 (z . relu(q)) sits in row 0 of the third tile: lanes 0..3.
-                const float den0 = __shfl_sync(0xffffffffu, o[2][0], q4);
-                const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
-                const float r0 = 1.0f / (den0 + a.eps);
-                const float r1 = 1.0f / (den1 + a.eps);
-                const int tok = warp * 16 + nt * 8 + q4 * 2;
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");   // the 32 x 128 output tile is complete
+            if (ok) {
+                const int tok0 = (c_begin + cidx) * kLaChunk;
 #pragma unroll
-                for (int mt = 0; mt < 2; ++mt) {
-                    const int i0 = mt * 16 + g;
-                    *reinterpret_cast<uint32_t*>(&stage[i0 * kLaOutLd + tok]) =
-                        pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
-                    *reinterpret_cast<uint32_t*>(&stage[(i0 + 8) * kLaOutLd + tok]) =
-                        pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
+                for (int rep = 0; rep < 2; ++rep) {
+                    const int idx = tid + rep * kLaWarps * 32;
+                    const int row = idx >> 4;
+                    const int c16 = idx & 15;
+                    const int tok = tok0 + c16 * 8;
+                    if (tok < a.n_tokens) {
+                        const uint4 w = *reinterpret_cast<const uint4*>(&stage[row * kLaOutLd + c16 * 8]);
+                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) +
+                                             static_cast<long long>(batch) * a.batch_stride +
+                                             static_cast<long long>(row0 + row) * a.ld + tok;
+                        *reinterpret_cast<uint4*>(dst) = w;
+                    }
                 }
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty[slot]);
-        asm volatile("bar.sync 1, 256;" ::: "memory");   // the 32 x 128 output tile is complete
-        if (ok) {
-            const int tok0 = (c_begin + cidx) * kLaChunk;
-#pragma unroll
-            for (int rep = 0; rep < 2; ++rep) {
-                const int idx = tid + rep * kLaWarps * 32;
-                const int row = idx >> 4;
-                const int c16 = idx & 15;
-                const int tok = tok0 + c16 * 8;
-                if (tok < a.n_tokens) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(&stage[row * kLaOutLd + c16 * 8]);
-                    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                                         static_cast<long long>(batch) * a.batch_stride +
-                                         static_cast<long long>(row0 + row) * a.ld + tok;
-                    *reinterpret_cast<uint4*>(dst) = w;
-                }
-            }
-        }
     }
     cluster.sync();
 }

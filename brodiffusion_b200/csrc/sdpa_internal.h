@@ -23,6 +23,16 @@ struct SdpaDevArgs {
     const float* key_scale;
     const float* val_scale;
     float scale_log2;  // softmax scale * log2(e)
+    // Traced / steered attention (hooks path): FP32 logit bias added to the scaled
+    // scores of queries [bias_row0, bias_row0 + bias_rows) x keys [0, bias_cols),
+    // and per-row softmax statistics (reference maximum in log2 units, row sum)
+    // written to lse[((batch * heads + head) * lq_total + query) * 2 + {0, 1}].
+    const float* bias;
+    int bias_row0, bias_rows, bias_cols;
+    long long bias_ld;
+    float bias_mul;     // 1 / softmax scale: the bias in raw-score units
+    float* lse;
+    int lq_total;
     // Fused all-gather: every output vector is also stored to the same offset of
     // these peer buffers (other GPUs' copies of the output tensor), per segment.
     int n_peers;
@@ -62,6 +72,25 @@ struct SdpaGeneralArgs {
 };
 cudaError_t launch_sdpa_general(const SdpaGeneralArgs& a, int num_heads, int batch, bool bf16,
                                 cudaStream_t stream);
+
+// Head-averaged attention map of a query-row range x leading key range.
+struct AttnMapArgs {
+    const void* q[2];
+    const void* k[2];
+    int q_rows[2], kv_rows[2];
+    long long q_ld[2], k_ld[2];
+    int num_heads, head_dim;
+    float scale_log2;
+    const float* lse;       // (heads, lq_total, 2)
+    int lq_total;
+    const float* bias;
+    int bias_row0, bias_rows, bias_cols;
+    long long bias_ld;
+    float* map;             // (map_rows, map_cols) FP32
+    int map_row0, map_rows, map_cols;
+    long long map_ld;
+};
+cudaError_t launch_attn_map(const AttnMapArgs& a, bool bf16, cudaStream_t stream);
 
 // Per-head RMSNorm + RoPE.
 struct NormRopeJobDev {
@@ -118,6 +147,9 @@ struct GemmProblem {
 };
 struct GemmArgs {
     GemmProblem p[3];
+    int n_tile_max;   // largest n_tile of the launch: sizes the shared-memory stages
+    int any_geglu;
+    int stages;
 };
 struct GemmLaunch {
     CUtensorMap tmA[3], tmB[3];

@@ -263,6 +263,18 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     }
                 }
             }
+            if constexpr (kHooks) {
+                if (a.bias != nullptr) {
+                    const int br = q_glob - a.bias_row0;
+                    if (br >= 0 && br < a.bias_rows && ti.kbase < a.bias_cols) {
+                        const float* brow = a.bias + static_cast<long long>(br) * a.bias_ld + ti.kbase;
+#pragma unroll
+                        for (int c = 0; c < kBN; ++c) {
+                            if (c < ti.valid && ti.kbase + c < a.bias_cols) s[c] += __ldg(brow + c) * a.bias_mul;
+                        }
+                    }
+                }
+            }
             int lim = ti.valid - 1;
             if (a.mask_mode == 1) lim = min(lim, q_glob + a.q_offset - ti.kbase);
             if (__any_sync(0xffffffffu, lim < kBN - 1)) {
@@ -360,6 +372,13 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
         const float inv = (l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
         const bool row_ok = ok && row_in_seg < seg_rows;
+        if constexpr (kHooks) {
+            if (a.lse != nullptr && row_ok) {
+                float* st = a.lse + ((static_cast<long long>(batch) * gridDim.y + head) * a.lq_total + q_glob) * 2;
+                st[0] = m_ref * sl2;
+                st[1] = l_sum;
+            }
+        }
         uint8_t* orow = nullptr;
         long long ooff = 0;      // byte offset of this row's head slice inside the output tensor
         if (row_ok) {
@@ -545,7 +564,7 @@ cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
 template <int HD, bool kBf16>
 cudaError_t launch_hd(const SdpaLaunch& L, cudaStream_t stream) {
     const bool hooks = L.args.key_mask != nullptr || L.args.key_scale != nullptr ||
-                       L.args.val_scale != nullptr;
+                       L.args.val_scale != nullptr || L.args.bias != nullptr || L.args.lse != nullptr;
     if (hooks) return launch_t<HD, kBf16, true, 0>(L, stream);
     switch (L.emu) {
         case 0: return launch_t<HD, kBf16, false, 0>(L, stream);

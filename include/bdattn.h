@@ -137,6 +137,43 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream);
 
+/* Traced / steered attention on the device.
+ *
+ * Replaces the host round trip of dit::joint_attention_traced
+ * (src/dit/common.cpp:198-329; include/brodiffusion/dit/common.h:117-129) and
+ * brotensor::cross_attention_forward_with_attn (src/unet_blocks.cpp:282-290):
+ *   - bias: optional FP32 (bias_rows, bias_cols) logit bias added to the
+ *     scaled scores of queries [bias_row0, bias_row0 + bias_rows) against keys
+ *     [0, bias_cols) before the softmax (for Flux: image rows x text keys,
+ *     src/dit/common.cpp:259-281; for the U-Net: every row x every key);
+ *   - attn_avg: optional FP32 output (map_rows, map_cols), the softmax of
+ *     queries [map_row0, map_row0 + map_rows) over keys [0, map_cols),
+ *     averaged over the heads — the block the callers keep
+ *     (src/dit/flux.cpp:505-508) instead of the full (L, L) map.
+ * Row indices count the concatenated query / key segments.  The attention
+ * output goes to p->o as usual.  workspace: bdattn_sdpa_traced_workspace_bytes
+ * bytes of device memory (per-row softmax statistics).  batch 1, head_dim <= 128.
+ */
+typedef struct bdattn_trace_params {
+    const float* bias;
+    int bias_row0;
+    int bias_rows;
+    int bias_cols;
+    long long bias_ld;      /* 0 => bias_cols */
+    float* attn_avg;
+    int map_row0;
+    int map_rows;
+    int map_cols;
+    long long map_ld;       /* 0 => map_cols */
+    void* workspace;
+    size_t workspace_bytes;
+} bdattn_trace_params;
+
+size_t bdattn_sdpa_traced_workspace_bytes(int num_heads, int q_rows_total);
+
+int bdattn_sdpa_traced_fwd(const bdattn_sdpa_params* p, const bdattn_trace_params* t,
+                           bdattn_stream_t stream);
+
 /* ------------------------------------------------- per-head RMSNorm + RoPE
  * out = rope(rms_norm_heads(x) * gain).  Replaces the headnorm view +
  * brotensor::rms_norm_forward (src/dit/flux.cpp:462-469,
