@@ -38,6 +38,8 @@ WORKLOADS = {
     "flux1024": (1, 512, 64, 64),
     "flux2048_headsharded": (2, 512, 128, 128),
 }
+# Sana 1600M ReLU linear attention (config 4): name -> (batch, heads, tokens); 1 GPU, HBM-bound.
+SANA_WORKLOADS = {"sana1024": (2, 70, 1024), "sana4096": (2, 70, 4096)}
 # dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_tc05_kernel launch
 # on the flux1024 workload, from the ncu capture summarised under profiles/.
 NCU_TRAFFIC_BYTES = {"flux1024": 84.99e6 + 6.07e6}
@@ -363,6 +365,69 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_sana(args):
+    """Config 4 on one GPU: one step = one bdattn_linear_attn_relu_fwd call on a
+    (batch, 2240, tokens) channel-major BF16 problem; metric = algorithmic GB/s
+    (4 * tokens * 2240 * 2 bytes per batch item).  Steps are replayed from a
+    CUDA graph so that host launch gaps do not enter the device time."""
+    import torch
+    import brodiffusion_b200 as bd
+    torch.cuda.set_device(0)
+    B, nh, N = SANA_WORKLOADS[args.workload]
+    Dm = nh * 32
+    byt = 4.0 * B * Dm * N * 2
+    n_sets = max(2, int(300e6 / byt) + 1)
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    sets = [tuple(torch.randn(B, Dm, N, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
+            for _ in range(n_sets)]
+    outs = [torch.empty(B, Dm, N, device="cuda", dtype=torch.bfloat16) for _ in range(n_sets)]
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        bd.linear_attn_relu_fwd(q, k, v, outs[i % n_sets], nh, 32)
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(args.steps):
+                step(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    t_end = time.perf_counter() + 0.3
+    while time.perf_counter() < t_end:        # keep the GPU busy while the clock sampler collects
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler.stop()
+    if bd.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure")
+    _, peak_gbs, kind = measured_peaks()
+    gbs = byt / (ms * 1e-3) / 1e9
+    line = {"metric": "linear-attention GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "batch": B, "heads": nh, "head_dim": 32, "tokens": N,
+                       "l2": f"rotating {n_sets} input sets ({n_sets * byt / 1e6:.0f} MB > 126 MB L2)",
+                       "timing": "CUDA-graph replay of the steps"},
+            "clocks": sampler.summary(), "gpu_launches": args.steps,
+            "roofline": {"bound": "hbm", "kernel": "linear_attn_kernel", "achieved": gbs, "peak": peak_gbs,
+                         "unit": "GB/s", "frac": gbs / peak_gbs, "peak_kind": f"{kind} copy bandwidth",
+                         "traffic": None}}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(L):
     """Oracle port of the reference attention core on the host cores, on a
     bounded sample of the same workload (about 10-20 s of CPU work)."""
@@ -395,7 +460,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS), default=None)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(SANA_WORKLOADS), default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
@@ -406,6 +471,11 @@ def main():
     if args.workload is None:
         args.workload = "flux1024" if max(world, args.gpus) == 1 else "flux2048_headsharded"
     args.warmup = max(args.warmup, 3)
+    if args.workload in SANA_WORKLOADS:
+        if args.impl == "reference" or world > 1:
+            raise SystemExit("the sana workloads run on one GPU with --impl ours")
+        run_sana(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
