@@ -371,22 +371,19 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             tc_fence_after();
         }
         const float inv = (l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
-        const bool row_ok = ok && row_in_seg < seg_rows;
         if constexpr (kHooks) {
-            if (a.lse != nullptr && row_ok) {
+            if (a.lse != nullptr && ok && row_in_seg < seg_rows) {
                 float* st = a.lse + ((static_cast<long long>(batch) * gridDim.y + head) * a.lq_total + q_glob) * 2;
                 st[0] = m_ref * sl2;
                 st[1] = l_sum;
             }
         }
-        uint8_t* orow = nullptr;
-        long long ooff = 0;      // byte offset of this row's head slice inside the output tensor
-        if (row_ok) {
-            ooff = 2 * (static_cast<long long>(batch) * (qseg ? a.o_bs[1] : a.o_bs[0]) +
-                        static_cast<long long>(row_in_seg) * (qseg ? a.o_ld[1] : a.o_ld[0]) +
-                        static_cast<long long>(head) * a.hd_out);
-            orow = reinterpret_cast<uint8_t*>(qseg ? a.o[1] : a.o[0]) + ooff;
-        }
+        // Epilogue: O / l goes through shared memory (this tile's Q buffer, no longer
+        // read: all Q.K^T MMAs have completed) so that global stores are whole
+        // rows: 16-byte chunk c of row r sits at chunk c ^ (r mod chunks) to keep
+        // the row-per-thread writes and the row-major reads free of bank conflicts.
+        constexpr int kRowChunks = HD / 8;
+        uint8_t* stg = smem_q + t * C::kQBytes;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
             uint32_t o[32];
@@ -397,22 +394,37 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 #pragma unroll
                 for (int i = 0; i < 32; ++i) o[i] = 0u;
             }
-            if (row_ok) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    if (c * 32 + g * 8 < a.hd_out) {
-                        uint4 w;
-                        w.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
-                        w.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
-                        w.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
-                        w.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + (c * 32 + g * 8) * 2) = w;
-                        // fused all-gather: the same vector goes to every peer's copy of
-                        // the output (plain stores over NVLink, no TMA, no multicast)
-                        for (int pi = 0; pi < a.n_peers; ++pi) {
-                            uint8_t* pb = reinterpret_cast<uint8_t*>(qseg ? a.o_peer[1][pi] : a.o_peer[0][pi]);
-                            *reinterpret_cast<uint4*>(pb + ooff + (c * 32 + g * 8) * 2) = w;
-                        }
+            for (int g = 0; g < 4; ++g) {
+                uint4 w;
+                w.x = pack2<kBf16>(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+                w.y = pack2<kBf16>(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+                w.z = pack2<kBf16>(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+                w.w = pack2<kBf16>(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+                const int cg = c * 4 + g;
+                *reinterpret_cast<uint4*>(stg + row_in_tile * (HD * 2) + ((cg ^ (row_in_tile & (kRowChunks - 1))) << 4)) = w;
+            }
+        }
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + t) : "memory");   // the 128 threads of this query tile
+        if (ok) {
+            uint8_t* obase = reinterpret_cast<uint8_t*>(qseg ? a.o[1] : a.o[0]);
+            const long long o_ld = qseg ? a.o_ld[1] : a.o_ld[0];
+            const long long o_bs = qseg ? a.o_bs[1] : a.o_bs[0];
+            const int out_chunks = a.hd_out >> 3;
+            for (int idx = row_in_tile; idx < kBM * kRowChunks; idx += kBM) {
+                const int r = idx / kRowChunks;
+                const int cg = idx - r * kRowChunks;
+                const int rs = qrow0 + t * kBM + r;
+                if (rs < seg_rows && cg < out_chunks) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(stg + r * (HD * 2) + ((cg ^ (r & (kRowChunks - 1))) << 4));
+                    const long long off = 2 * (static_cast<long long>(batch) * o_bs + static_cast<long long>(rs) * o_ld +
+                                               static_cast<long long>(head) * a.hd_out + cg * 8);
+                    *reinterpret_cast<uint4*>(obase + off) = w;
+                    // fused all-gather: the same vector goes to every peer's copy of the
+                    // output (plain stores over NVLink; no TMA, no multicast, no peer reads)
+                    for (int pi = 0; pi < a.n_peers; ++pi) {
+                        uint8_t* pb = reinterpret_cast<uint8_t*>(qseg ? a.o_peer[1][pi] : a.o_peer[0][pi]);
+                        *reinterpret_cast<uint4*>(pb + off) = w;
                     }
                 }
             }
@@ -532,7 +544,6 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
     }
 
-    if (a.n_peers > 0) __threadfence_system();   // peer stores are performed before the kernel retires
     tc_fence_before();
     __syncthreads();
     if (warp == 8) {
