@@ -75,6 +75,20 @@ class TraceParams(C.Structure):
     ]
 
 
+class QkvProjParams(C.Structure):
+    """Mirror of ``bdattn_qkv_proj_params`` (include/bdattn.h)."""
+    _fields_ = [
+        ("dtype", C.c_int), ("num_heads", C.c_int), ("head_dim", C.c_int),
+        ("x", C.c_void_p), ("rows", C.c_int), ("in_features", C.c_int), ("x_ld", C.c_longlong),
+        ("wq", C.c_void_p), ("wk", C.c_void_p), ("wv", C.c_void_p),
+        ("bq", C.c_void_p), ("bk", C.c_void_p), ("bv", C.c_void_p),
+        ("gain_q", C.c_void_p), ("gain_k", C.c_void_p), ("gain_dtype", C.c_int), ("eps", C.c_float),
+        ("cos", C.c_void_p), ("sin", C.c_void_p), ("rope_row0", C.c_int),
+        ("q_out", C.c_void_p), ("k_out", C.c_void_p), ("v_out", C.c_void_p),
+        ("q_ld", C.c_longlong), ("k_ld", C.c_longlong), ("v_ld", C.c_longlong),
+    ]
+
+
 class QkvoParams(C.Structure):
     """Mirror of ``bdattn_qkvo_params`` (include/bdattn.h)."""
     _fields_ = [
@@ -135,6 +149,7 @@ def lib():
         L.bdattn_qkvo_fwd.argtypes = [C.POINTER(QkvoParams), C.c_void_p]
         L.bdattn_qkvo_static_capacity.restype = C.c_size_t
         L.bdattn_qkvo_fwd_static.argtypes = [C.POINTER(QkvoParams), C.c_void_p]
+        L.bdattn_qkv_norm_rope_fwd.argtypes = [C.POINTER(QkvProjParams), C.c_void_p]
         L.bdattn_project_kv.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_longlong, C.c_void_p,
                                         C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_longlong, C.c_int, C.c_int, C.c_void_p]
@@ -423,3 +438,25 @@ def sdpa_traced_fwd(q, k, v, out, num_heads, *, bias=None, bias_row0=0, map_row0
     t.workspace, t.workspace_bytes = ws.data_ptr(), ws.numel()
     sdpa_fwd(q, k, v, out, num_heads, mask_mode=mask_mode, key_mask=key_mask, stream=stream, _trace=t)
     return amap
+
+
+def qkv_norm_rope_fwd(x, wq, wk, wv, q_out, k_out, v_out, num_heads, head_dim, *, gain_q=None,
+                      gain_k=None, cos=None, sin=None, rope_row0=0, eps=1e-6, bq=None, bk=None,
+                      bv=None, stream=None):
+    """``bdattn_qkv_norm_rope_fwd``: Q/K/V projections with per-head RMSNorm and
+    RoPE in the GEMM epilogue."""
+    p = QkvProjParams()
+    p.dtype, p.num_heads, p.head_dim = _dtype_code(x), num_heads, head_dim
+    p.x, p.rows, p.in_features, p.x_ld = x.data_ptr(), x.shape[0], x.shape[1], x.stride(0)
+    p.wq, p.wk, p.wv = _ptr(wq), _ptr(wk), _ptr(wv)
+    p.bq, p.bk, p.bv = _ptr(bq), _ptr(bk), _ptr(bv)
+    p.gain_q, p.gain_k = _ptr(gain_q), _ptr(gain_k)
+    g = gain_q if gain_q is not None else gain_k
+    p.gain_dtype = _dtype_code(g) if g is not None else F32
+    p.eps = eps
+    p.cos, p.sin, p.rope_row0 = _ptr(cos), _ptr(sin), rope_row0
+    p.q_out, p.k_out, p.v_out = _ptr(q_out), _ptr(k_out), _ptr(v_out)
+    p.q_ld = q_out.stride(0) if q_out is not None else 0
+    p.k_ld = k_out.stride(0) if k_out is not None else 0
+    p.v_ld = v_out.stride(0) if v_out is not None else 0
+    _check(lib().bdattn_qkv_norm_rope_fwd(C.byref(p), _stream(stream)))

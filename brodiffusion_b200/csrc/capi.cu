@@ -188,16 +188,14 @@ int add_gemm_problem(const char* op, bdattn::GemmLaunch& L, int idx, const void*
         p.tiles_n = N / head_dim;
     } else {
         if (N % 8 != 0) return fail("%s: output width must be a multiple of 8 (got %d)", op, N);
-        p.n_tile = 64;
-        p.n_step = 64;
-        p.n_valid = 64;
-        p.c_step = 64;
-        p.c_fill = 64;
-        p.tiles_n = (N + 63) / 64;
-        if (N % 64 != 0) {
-            // last tile is ragged: the epilogue stores only columns below N
-            p.c_fill = 64;
-        }
+        // 128-column tiles once the output is wide enough to fill the SMs with them
+        const int tile = (geglu_offset == 0 && static_cast<long long>((M + 127) / 128) * ((N + 127) / 128) >= 148) ? 128 : 64;
+        p.n_tile = tile;
+        p.n_step = tile;
+        p.n_valid = tile;
+        p.c_step = tile;
+        p.c_fill = tile;      // the epilogue stops at the matrix edge on a ragged last tile
+        p.tiles_n = (N + tile - 1) / tile;
     }
     if (make_map_2d(op, &L.tmA[idx], A, L.bf16, K, M, lda, 128)) return -1;
     // the weight matrix has N (+ D_out for GEGLU) rows
@@ -622,6 +620,49 @@ int bdattn_linear_fwd(const void* x, const void* w, const void* bias, void* y, i
     L.bf16 = dtype == BDATTN_BF16;
     if (add_gemm_problem(op, L, 0, x, ldx, w, ldw, bias, y, ldy, M, N, K, 0, 0, 0)) return -1;
     finish_gemm_launch(L, 1);
+    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
+int bdattn_qkv_norm_rope_fwd(const bdattn_qkv_proj_params* p, bdattn_stream_t stream) {
+    const char* op = "bdattn_qkv_norm_rope_fwd";
+    if (p == nullptr) return fail("%s: params is null", op);
+    if (require_sm100(op)) return -1;
+    if (p->dtype != BDATTN_BF16 && p->dtype != BDATTN_F16) return fail("%s: dtype must be BF16 or F16", op);
+    if (p->head_dim != 64 && p->head_dim != 128) return fail("%s: head_dim must be 64 or 128 (got %d)", op, p->head_dim);
+    if (p->num_heads < 1 || p->rows < 1 || p->in_features < 1) return fail("%s: empty problem", op);
+    if ((p->cos == nullptr) != (p->sin == nullptr)) return fail("%s: cos and sin must both be given", op);
+    if (p->gain_q != nullptr || p->gain_k != nullptr)
+        if (p->gain_dtype != BDATTN_F32 && p->gain_dtype != p->dtype)
+            return fail("%s: gain_dtype must be F32 or the tensor dtype", op);
+    const int N = p->num_heads * p->head_dim;
+    bdattn::GemmLaunch L;
+    std::memset(&L, 0, sizeof(L));
+    L.bf16 = p->dtype == BDATTN_BF16;
+    const void* w[3] = {p->wq, p->wk, p->wv};
+    const void* b[3] = {p->bq, p->bk, p->bv};
+    void* out[3] = {p->q_out, p->k_out, p->v_out};
+    const long long ld[3] = {p->q_ld > 0 ? p->q_ld : N, p->k_ld > 0 ? p->k_ld : N, p->v_ld > 0 ? p->v_ld : N};
+    const void* gain[3] = {p->gain_q, p->gain_k, nullptr};
+    int n = 0;
+    for (int i = 0; i < 3; ++i) {
+        if (w[i] == nullptr || out[i] == nullptr) continue;     // a projection may be left out
+        if (add_gemm_problem(op, L, n, p->x, p->x_ld > 0 ? p->x_ld : p->in_features, w[i], p->in_features, b[i],
+                             out[i], ld[i], p->rows, N, p->in_features, p->head_dim, p->head_dim, 0))
+            return -1;
+        bdattn::GemmProblem& g = L.args.p[n];
+        g.norm_rope = 1;
+        g.gain = gain[i];
+        g.gain_is_f32 = p->gain_dtype == BDATTN_F32 ? 1 : 0;
+        g.eps = p->eps;
+        g.cos = i < 2 ? p->cos : nullptr;
+        g.sin = i < 2 ? p->sin : nullptr;
+        g.rope_row0 = p->rope_row0;
+        ++n;
+    }
+    if (n == 0) return fail("%s: no projection requested", op);
+    finish_gemm_launch(L, n);
     cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;

@@ -147,7 +147,78 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         const int n_valid = min(p.n_valid, p.N - n0);
         // plain tiles stop at the matrix edge; head tiles own their padded slot
         const int c_lim = p.c_step == p.n_step ? min(p.c_fill, p.N - n0) : p.c_fill;
-        if (ok) {
+        if (ok && p.norm_rope) {
+            // The tile is one head and this thread holds one token's row of it:
+            // RMSNorm over the head and the rotary embedding are thread-local
+            // (src/dit/flux.cpp:462-469 + src/dit/common.cpp:192-193 fused into
+            // the projection, so Q and K never travel to HBM un-normalised).
+            float f[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                if (c * 32 < p.n_tile) {
+                    uint32_t v[32];
+                    tmem_ld32(tacc + c * 32, v);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __uint_as_float(v[i]);
+                        if (p.bias != nullptr) {
+                            const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + c * 32 + i];
+                            x += kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                       : __half2float(*reinterpret_cast<const __half*>(&b));
+                        }
+                        f[c * 32 + i] = x;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) f[c * 32 + i] = 0.0f;
+                }
+            }
+            if (p.gain != nullptr) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int i = 0; i < 128; ++i) ss = fmaf(f[i], f[i], ss);
+                const float inv = rsqrtf(ss / static_cast<float>(p.n_tile) + p.eps);
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    if (i < p.n_tile) {
+                        float gv;
+                        if (p.gain_is_f32) gv = __ldg(reinterpret_cast<const float*>(p.gain) + i);
+                        else {
+                            const uint16_t b = reinterpret_cast<const uint16_t*>(p.gain)[i];
+                            gv = kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                       : __half2float(*reinterpret_cast<const __half*>(&b));
+                        }
+                        f[i] *= inv * gv;
+                    }
+                }
+            }
+            if (p.cos != nullptr && row < p.M) {
+                const long long t = static_cast<long long>(p.rope_row0 + row) * (p.n_tile / 2);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    if (2 * i < p.n_tile) {
+                        const float cv = __ldg(p.cos + t + i), sv = __ldg(p.sin + t + i);
+                        const float a0 = f[2 * i], b0 = f[2 * i + 1];
+                        f[2 * i] = a0 * cv - b0 * sv;
+                        f[2 * i + 1] = a0 * sv + b0 * cv;
+                    }
+                }
+            }
+            if (row < p.M) {
+#pragma unroll
+                for (int v8 = 0; v8 < 16; ++v8) {
+                    if (v8 * 8 < p.n_tile) {
+                        uint4 w;
+                        w.x = pack2<kBf16>(f[v8 * 8 + 0], f[v8 * 8 + 1]);
+                        w.y = pack2<kBf16>(f[v8 * 8 + 2], f[v8 * 8 + 3]);
+                        w.z = pack2<kBf16>(f[v8 * 8 + 4], f[v8 * 8 + 5]);
+                        w.w = pack2<kBf16>(f[v8 * 8 + 6], f[v8 * 8 + 7]);
+                        *reinterpret_cast<uint4*>(crow + v8 * 8) = w;
+                    }
+                }
+            }
+        } else if (ok) {
             for (int c = 0; c < c_lim; c += 32) {
                 uint32_t v[32], gt[32];
                 if (c < p.n_tile) {

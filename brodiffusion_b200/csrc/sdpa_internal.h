@@ -144,6 +144,14 @@ struct GemmProblem {
     int c_step;         // output columns between tile starts
     int c_fill;         // output columns written per tile (zeros beyond n_valid)
     int geglu_offset;   // 0, or D_out
+    // Per-head RMSNorm + RoPE epilogue (head tiles with n_tile == head_dim only):
+    const void* gain;   // head_dim values, or null
+    int gain_is_f32;
+    float eps;
+    const float* cos;   // (rows, head_dim / 2) tables, or null
+    const float* sin;
+    int rope_row0;
+    int norm_rope;      // 1: run the per-head epilogue
 };
 struct GemmArgs {
     GemmProblem p[3];

@@ -375,6 +375,50 @@ int bdattn_linear_fwd(const void* x, const void* w, const void* bias, void* y, i
                       int N, int K, long long ldx, long long ldw, long long ldy,
                       bdattn_stream_t stream);
 
+/* Q/K/V projections with the per-head RMSNorm and RoPE fused into the GEMM
+ * epilogue: one launch replaces lin_(to_q), lin_(to_k), lin_(to_v)
+ * (src/dit/flux.cpp:471-473,590-592, src/dit/qwenimage21_forward.cpp:579-581),
+ * the two headnorm calls (flux.cpp:474-475, qwenimage21_forward.cpp:582-583)
+ * and the two rope_apply calls (src/dit/common.cpp:192-193,
+ * qwenimage21_forward.cpp:584-585) of one token stream.
+ *   x (rows, in_features); wq/wk/wv (num_heads*head_dim, in_features), biases
+ *   optional; gain_q / gain_k: head_dim values (gain_dtype F32 or the tensor
+ *   dtype) or NULL; cos/sin FP32 (>= rope_row0 + rows, head_dim/2) or NULL;
+ *   q_out, k_out receive rope(rmsnorm(x W^T + b) * gain), v_out the plain
+ *   projection; a NULL weight or output skips that projection.
+ * head_dim 64 or 128: each GEMM tile is one head, so the norm and the rotation
+ * are local to the thread that holds a token's row of the accumulator. */
+typedef struct bdattn_qkv_proj_params {
+    int dtype;
+    int num_heads;
+    int head_dim;
+    const void* x;
+    int rows;
+    int in_features;
+    long long x_ld;        /* 0 => in_features */
+    const void* wq;
+    const void* wk;
+    const void* wv;
+    const void* bq;
+    const void* bk;
+    const void* bv;
+    const void* gain_q;
+    const void* gain_k;
+    int gain_dtype;
+    float eps;
+    const float* cos;
+    const float* sin;
+    int rope_row0;
+    void* q_out;
+    void* k_out;
+    void* v_out;
+    long long q_ld;        /* 0 => num_heads * head_dim */
+    long long k_ld;
+    long long v_ld;
+} bdattn_qkv_proj_params;
+
+int bdattn_qkv_norm_rope_fwd(const bdattn_qkv_proj_params* p, bdattn_stream_t stream);
+
 int bdattn_linear_geglu_fwd(const void* x, const void* w, const void* bias, void* y, int dtype,
                             int rows, int d_in, int d_out, bdattn_stream_t stream);
 
