@@ -7,6 +7,7 @@
 #include "linear_attn.cu"
 #include "rope_tables.cu"
 #include "gemm_tc05.cu"
+#include "gemm_wide.cu"
 #include "elementwise.cu"
 #include "attn_map.cu"
 #include "capi.cu"

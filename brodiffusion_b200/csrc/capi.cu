@@ -201,6 +201,10 @@ int add_gemm_problem(const char* op, bdattn::GemmLaunch& L, int idx, const void*
     // the weight matrix has N (+ D_out for GEGLU) rows
     const long long w_rows = geglu_offset > 0 ? static_cast<long long>(N) + geglu_offset : N;
     if (make_map_2d(op, &L.tmB[idx], W, L.bf16, K, w_rows, ldw, p.n_tile)) return -1;
+    // 128 x 256 tiles need whole tiles along N and, for head tiles, unpadded heads of 64 or 128
+    L.wide[idx] = geglu_offset == 0 && N % 256 == 0 &&
+                  (head_dim == 0 || (head_dim == head_pad && (head_dim == 64 || head_dim == 128)));
+    if (L.wide[idx] && make_map_2d(op, &L.tmBw[idx], W, L.bf16, K, w_rows, ldw, 256)) return -1;
     return 0;
 }
 
@@ -212,6 +216,8 @@ void finish_gemm_launch(bdattn::GemmLaunch& L, int n) {
         L.args.p[i].tiles_n = 0;
         L.tmA[i] = L.tmA[0];
         L.tmB[i] = L.tmB[0];
+        L.tmBw[i] = L.tmBw[0];
+        L.wide[i] = L.wide[0];
     }
 }
 
@@ -620,7 +626,7 @@ int bdattn_linear_fwd(const void* x, const void* w, const void* bias, void* y, i
     L.bf16 = dtype == BDATTN_BF16;
     if (add_gemm_problem(op, L, 0, x, ldx, w, ldw, bias, y, ldy, M, N, K, 0, 0, 0)) return -1;
     finish_gemm_launch(L, 1);
-    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = bdattn::launch_gemm(L, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }
@@ -633,6 +639,7 @@ int bdattn_qkv_norm_rope_fwd(const bdattn_qkv_proj_params* p, bdattn_stream_t st
     if (p->head_dim != 64 && p->head_dim != 128) return fail("%s: head_dim must be 64 or 128 (got %d)", op, p->head_dim);
     if (p->num_heads < 1 || p->rows < 1 || p->in_features < 1) return fail("%s: empty problem", op);
     if ((p->cos == nullptr) != (p->sin == nullptr)) return fail("%s: cos and sin must both be given", op);
+    if (!aligned16(p->cos) || !aligned16(p->sin)) return fail("%s: cos and sin must be 16-byte aligned", op);
     if (p->gain_q != nullptr || p->gain_k != nullptr)
         if (p->gain_dtype != BDATTN_F32 && p->gain_dtype != p->dtype)
             return fail("%s: gain_dtype must be F32 or the tensor dtype", op);
@@ -663,7 +670,7 @@ int bdattn_qkv_norm_rope_fwd(const bdattn_qkv_proj_params* p, bdattn_stream_t st
     }
     if (n == 0) return fail("%s: no projection requested", op);
     finish_gemm_launch(L, n);
-    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = bdattn::launch_gemm(L, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }
@@ -678,7 +685,7 @@ int bdattn_linear_geglu_fwd(const void* x, const void* w, const void* bias, void
     L.bf16 = dtype == BDATTN_BF16;
     if (add_gemm_problem(op, L, 0, x, d_in, w, d_in, bias, y, d_out, rows, d_out, d_in, 0, 0, d_out)) return -1;
     finish_gemm_launch(L, 1);
-    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = bdattn::launch_gemm(L, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }
@@ -729,7 +736,7 @@ int bdattn_project_kv(const void* ctx, int ctx_rows, int ctx_cols, long long ctx
     if (add_gemm_problem(op, L, 0, ctx, ctx_ld, wk, ctx_cols, bk, k_out, kv_ld, ctx_rows, inner_dim, ctx_cols, 0, 0, 0)) return -1;
     if (add_gemm_problem(op, L, 1, ctx, ctx_ld, wv, ctx_cols, bv, v_out, kv_ld, ctx_rows, inner_dim, ctx_cols, 0, 0, 0)) return -1;
     finish_gemm_launch(L, 2);
-    cudaError_t e = bdattn::launch_gemm_tc05(L, reinterpret_cast<cudaStream_t>(stream));
+    cudaError_t e = bdattn::launch_gemm(L, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }
@@ -788,7 +795,7 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
                                  pad ? hd : 0, P, 0)) return -1;
         }
         finish_gemm_launch(L, n);
-        cudaError_t e = bdattn::launch_gemm_tc05(L, st);
+        cudaError_t e = bdattn::launch_gemm(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
     }
     const void* Kin = Kp;
@@ -855,7 +862,7 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
         if (add_gemm_problem(op, L, 0, Op, C, p->wo, C, p->bo, p->out, p->out_ld > 0 ? p->out_ld : out_cols, Lq,
                              out_cols, C, 0, 0, 0)) return -1;
         finish_gemm_launch(L, 1);
-        cudaError_t e = bdattn::launch_gemm_tc05(L, st);
+        cudaError_t e = bdattn::launch_gemm(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
     }
     return 0;

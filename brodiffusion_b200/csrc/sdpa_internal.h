@@ -161,11 +161,19 @@ struct GemmArgs {
 };
 struct GemmLaunch {
     CUtensorMap tmA[3], tmB[3];
+    CUtensorMap tmBw[3];   // weight maps with 256-row boxes (wide-tile kernel), valid where wide[i]
+    bool wide[3];          // problem i can run as 128 x 256 tiles
     GemmArgs args;
     int n_problems;
     bool bf16;
 };
 cudaError_t launch_gemm_tc05(const GemmLaunch& L, cudaStream_t stream);
+// Persistent 128 x 256-tile kernel; every problem of the launch must have wide[i] set.
+cudaError_t launch_gemm_wide(const GemmLaunch& L, cudaStream_t stream);
+int gemm_wide_tiles(const GemmLaunch& L);
+// Picks the wide-tile kernel when every problem allows it and there is at least
+// one wide tile per SM, the one-tile-per-CTA kernel otherwise.
+cudaError_t launch_gemm(const GemmLaunch& L, cudaStream_t stream);
 
 // Elementwise helpers.
 cudaError_t launch_add_inplace(void* y, const void* x, long long n, bool bf16, cudaStream_t stream);

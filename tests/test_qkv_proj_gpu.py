@@ -59,6 +59,68 @@ def test_fused_projection_feeds_attention(bd, oracle):
     G.check(G.host(out), ref, max_abs=3e-2, what="projection + attention")
 
 
+def test_wide_tile_projection_matches_oracle(bd, oracle):
+    """Large enough for the persistent 128 x 256-tile kernel: 18 row tiles x 4
+    column tiles x 3 projections = 216 tiles (more than one per SM, so some CTAs
+    walk two tiles and the stage ring and both accumulators wrap); two heads of
+    128 per tile, five K blocks with a ragged last one."""
+    rows, din, nh, hd = 2304 - 5, 296, 8, 128
+    D = nh * hd
+    x = synth.activations((rows, din), 9500)
+    wq, wk, wv = (synth.round_bf16(synth.normal((D, din), 9501 + i, 0, 0.06)) for i in range(3))
+    bk = synth.weights((D,), 9510)
+    gq, gk = synth.gains(hd, 9511, "f32"), synth.gains(hd, 9512, "f32")
+    cos, sin = oracle.flux_rope_tables(256, 48, 48, hd)      # 2560 table rows
+    q = torch.full((rows, D), float("nan"), device="cuda", dtype=torch.bfloat16)
+    k, v = torch.full_like(q, float("nan")), torch.full_like(q, float("nan"))
+    bd.qkv_norm_rope_fwd(G.dev(x), G.dev(wq), G.dev(wk), G.dev(wv), q, k, v, nh, hd,
+                         gain_q=G.dev(gq, torch.float32), gain_k=G.dev(gk, torch.float32),
+                         cos=G.dev(cos, torch.float32), sin=G.dev(sin, torch.float32), rope_row0=3,
+                         bk=G.dev(bk))
+    assert bd.device_status() == 0
+    rq = oracle.rope_apply(oracle.rms_norm_heads(oracle.linear(x, wq), nh, hd, gq), nh, hd, cos[3:], sin[3:])
+    rk = oracle.rope_apply(oracle.rms_norm_heads(oracle.linear(x, wk, bk), nh, hd, gk), nh, hd, cos[3:], sin[3:])
+    rv = oracle.linear(x, wv)
+    assert np.abs(G.host(q) - rq).max() < 2.5e-2
+    assert np.abs(G.host(k) - rk).max() < 2.5e-2
+    G.check(G.host(v), rv, max_abs=2.5e-2, what="V projection (wide tiles)")
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("hd", [0, 64])
+def test_wide_tile_linear_matches_oracle(bd, oracle, dtype, hd):
+    """Plain linear layer (hd 0, 162 tiles) and four heads of 64 per tile
+    (3 x 72 tiles), FP16 and BF16, bias, K not a multiple of 64."""
+    tdt = torch.bfloat16 if dtype == "bf16" else torch.float16
+    rnd = synth.round_bf16 if dtype == "bf16" else (lambda a: a.astype(np.float16).astype(np.float32))
+    if hd == 0:
+        rows, din, N = 2300, 200, 2304
+        x = rnd(synth.normal((rows, din), 9600, 0, 1.0))
+        w = rnd(synth.normal((N, din), 9601, 0, 0.06))
+        b = rnd(synth.normal((N,), 9602, 0, 0.5))
+        y = torch.full((rows, N), float("nan"), device="cuda", dtype=tdt)
+        bd.linear_fwd(G.dev(x, tdt), G.dev(w, tdt), G.dev(b, tdt), y)
+        assert bd.device_status() == 0
+        G.check(G.host(y), oracle.linear(x, w, b), max_abs=2.5e-2, what="linear (wide tiles)")
+    else:
+        rows, din, nh = 2304, 136, 16
+        D = nh * hd
+        x = rnd(synth.normal((rows, din), 9610, 0, 1.0))
+        ws = [rnd(synth.normal((D, din), 9611 + i, 0, 0.06)) for i in range(3)]
+        g = synth.gains(hd, 9620, "f32")
+        cos, sin = oracle.flux_rope_tables(256, 48, 48, hd, (8, 28, 28))
+        outs = [torch.full((rows, D), float("nan"), device="cuda", dtype=tdt) for _ in range(3)]
+        tg = G.dev(g, torch.float32)
+        bd.qkv_norm_rope_fwd(G.dev(x, tdt), *[G.dev(w, tdt) for w in ws], *outs, nh, hd, gain_q=tg, gain_k=tg,
+                             cos=G.dev(cos, torch.float32), sin=G.dev(sin, torch.float32))
+        assert bd.device_status() == 0
+        for i in range(3):
+            ref = oracle.linear(x, ws[i])
+            if i < 2:
+                ref = oracle.rope_apply(oracle.rms_norm_heads(ref, nh, hd, g), nh, hd, cos, sin)
+            assert np.abs(G.host(outs[i]) - ref).max() < 2.5e-2
+
+
 def test_errors(bd):
     x = torch.zeros(8, 64, device="cuda", dtype=torch.bfloat16)
     w = torch.zeros(80, 64, device="cuda", dtype=torch.bfloat16)
