@@ -46,6 +46,7 @@ class SdpaParams(C.Structure):
         ("mask_mode", C.c_int),
         ("key_mask", C.c_void_p), ("key_scale", C.c_void_p), ("val_scale", C.c_void_p),
         ("softmax_scale", C.c_float),
+        ("num_kv_heads", C.c_int),
     ]
 
 
@@ -159,6 +160,8 @@ def lib():
         L.bdattn_linear_geglu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                               C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.bdattn_add_inplace.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p]
+        L.bdattn_axpby_inplace.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_float, C.c_float,
+                                           C.c_int, C.c_void_p]
         L.bdattn_add_row_bias.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_longlong,
                                           C.c_int, C.c_void_p]
         _lib = L
@@ -213,7 +216,8 @@ def device_status(clear: bool = True) -> int:
 
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
-             val_scale=None, softmax_scale=0.0, stream=None, peer_out_ptrs=None, _trace=None):
+             val_scale=None, softmax_scale=0.0, num_kv_heads=0, stream=None, peer_out_ptrs=None,
+             _trace=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
     (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
@@ -253,6 +257,7 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
     p.key_scale = key_scale.data_ptr() if key_scale is not None else None
     p.val_scale = val_scale.data_ptr() if val_scale is not None else None
     p.softmax_scale = softmax_scale
+    p.num_kv_heads = num_kv_heads
     if _trace is not None:
         _check(lib().bdattn_sdpa_traced_fwd(C.byref(p), C.byref(_trace), _stream(stream)))
         return
@@ -406,6 +411,14 @@ def add_inplace(y, x, *, stream=None):
         raise BdattnError("add_inplace_vec: Y and X must be dense and of equal shape")
     _check(lib().bdattn_add_inplace(y.data_ptr(), x.data_ptr(), y.numel(), _dtype_code(y),
                                     _stream(stream)))
+
+
+def axpby_inplace(y, x, a, b=0.0, *, stream=None):
+    """``bdattn_axpby_inplace``: y = a*y + b*x in place (x may be None: y = a*y).
+    The prefix-cache ``scale_kv`` / ``blend_from`` operations."""
+    if not y.is_contiguous() or (x is not None and (x.shape != y.shape or not x.is_contiguous())):
+        raise BdattnError("axpby_inplace: Y and X must be dense and of equal shape")
+    _check(lib().bdattn_axpby_inplace(y.data_ptr(), _ptr(x), y.numel(), a, b, _dtype_code(y), _stream(stream)))
 
 
 def add_row_bias(y, bias, *, stream=None):

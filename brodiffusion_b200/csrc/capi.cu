@@ -263,6 +263,10 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
     if (p->mask_mode != BDATTN_MASK_NONE && p->mask_mode != BDATTN_MASK_CAUSAL)
         return fail("%s: unknown mask_mode %d", op, p->mask_mode);
     const long long D = static_cast<long long>(p->num_heads) * hd;
+    const int nkv = p->num_kv_heads > 0 ? p->num_kv_heads : p->num_heads;
+    if (p->num_kv_heads < 0 || p->num_heads % nkv != 0)
+        return fail("%s: num_kv_heads must divide num_heads (got %d and %d)", op, p->num_kv_heads, p->num_heads);
+    const long long Dkv = static_cast<long long>(nkv) * hd;
     long long Lq = 0, Lk = 0;
     for (int s = 0; s < p->n_q_seg; ++s) {
         if (p->q[s] == nullptr || p->o[s] == nullptr) return fail("%s: q/o segment %d is null", op, s);
@@ -278,8 +282,8 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
     for (int s = 0; s < p->n_kv_seg; ++s) {
         if (p->k[s] == nullptr || p->v[s] == nullptr) return fail("%s: k/v segment %d is null", op, s);
         if (p->kv_rows[s] < 1) return fail("%s: kv_rows[%d] must be >= 1", op, s);
-        if (p->k_ld[s] < D || p->v_ld[s] < D)
-            return fail("%s: k_ld/v_ld of segment %d smaller than num_heads*head_dim", op, s);
+        if (p->k_ld[s] < Dkv || p->v_ld[s] < Dkv)
+            return fail("%s: k_ld/v_ld of segment %d smaller than num_kv_heads*head_dim", op, s);
         if (p->k_ld[s] % 8 || p->v_ld[s] % 8 || !aligned16(p->k[s]) || !aligned16(p->v[s]) ||
             p->k_batch_stride[s] % 8 || p->v_batch_stride[s] % 8)
             return fail("%s: k/v segment %d must be 16-byte aligned with strides that are multiples of 8 "
@@ -302,10 +306,10 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
             if (make_map_heads(op, &L.tmQ[s], p->q[qs], bf16, hd, p->num_heads, p->q_rows[qs], p->batch,
                                p->q_ld[qs], p->q_batch_stride[qs], 128))
                 return -1;
-            if (make_map_heads(op, &L.tmK[s], p->k[ks], bf16, hd, p->num_heads, p->kv_rows[ks], p->batch,
+            if (make_map_heads(op, &L.tmK[s], p->k[ks], bf16, hd, nkv, p->kv_rows[ks], p->batch,
                                p->k_ld[ks], p->k_batch_stride[ks], 128))
                 return -1;
-            if (make_map_heads(op, &L.tmV[s], p->v[ks], bf16, hd, p->num_heads, p->kv_rows[ks], p->batch,
+            if (make_map_heads(op, &L.tmV[s], p->v[ks], bf16, hd, nkv, p->kv_rows[ks], p->batch,
                                p->v_ld[ks], p->v_batch_stride[ks], 128))
                 return -1;
         }
@@ -326,6 +330,7 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         a.mask_mode = p->mask_mode;
         a.q_offset = static_cast<int>(Lk - Lq);
         a.hd_out = hd;
+        a.kv_group = p->num_heads / nkv;
         a.key_mask = p->key_mask;
         a.key_scale = p->key_scale;
         a.val_scale = p->val_scale;
@@ -380,6 +385,7 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
     g.mask_mode = p->mask_mode;
     g.q_offset = static_cast<int>(Lk - Lq);
     g.head_dim = hd;
+    g.kv_group = p->num_heads / nkv;
     g.key_mask = p->key_mask;
     g.key_scale = p->key_scale;
     g.val_scale = p->val_scale;
@@ -423,6 +429,8 @@ int bdattn_sdpa_traced_fwd(const bdattn_sdpa_params* p, const bdattn_trace_param
             return fail("%s: map block (rows %d..%d, %d cols) does not fit the %lld x %lld score matrix", op,
                         t->map_row0, t->map_row0 + t->map_rows, t->map_cols, Lq, Lk);
     }
+    if (p->num_kv_heads > 0 && p->num_kv_heads != p->num_heads)
+        return fail("%s: grouped-query heads are not supported by the traced path", op);
     const size_t need = bdattn_sdpa_traced_workspace_bytes(p->num_heads, static_cast<int>(Lq));
     if (t->workspace == nullptr || t->workspace_bytes < need)
         return fail("%s: workspace of %zu bytes needed (got %zu)", op, need, t->workspace_bytes);
@@ -701,6 +709,19 @@ int bdattn_add_inplace(void* y, const void* x, long long n, int dtype, bdattn_st
     return 0;
 }
 
+int bdattn_axpby_inplace(void* y, const void* x, long long n, float a, float b, int dtype,
+                         bdattn_stream_t stream) {
+    const char* op = "axpby_inplace";
+    if (require_sm100(op)) return -1;
+    if (dtype != BDATTN_BF16 && dtype != BDATTN_F16) return fail("%s: tensors must be FP16 or BF16", op);
+    if (y == nullptr || n < 0) return fail("%s: bad arguments", op);
+    if (x == nullptr && b != 0.0f) return fail("%s: x is null but b is not zero", op);
+    if (n == 0 || (a == 1.0f && (x == nullptr || b == 0.0f))) return 0;
+    cudaError_t e = bdattn::launch_axpby_inplace(y, x, n, a, b, dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return cuda_fail(op, e);
+    return 0;
+}
+
 int bdattn_add_row_bias(void* y, const void* bias, int rows, int cols, long long ld, int dtype,
                         bdattn_stream_t stream) {
     const char* op = "add_inplace_row_bias";
@@ -832,6 +853,7 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
         a.mask_mode = p->causal ? 1 : 0;
         a.q_offset = Lk - Lq;
         a.hd_out = hd;
+        a.kv_group = 1;
         a.key_mask = p->key_mask;
         a.scale_log2 = scale * 1.4426950408889634f;
         L.q_ctas = a.q_ctas0;
@@ -847,6 +869,7 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
         g.mask_mode = p->causal ? 1 : 0;
         g.q_offset = Lk - Lq;
         g.head_dim = hd;
+        g.kv_group = 1;
         g.key_mask = p->key_mask;
         g.scale = scale;
         cudaError_t e = bdattn::launch_sdpa_general(g, nh, 1, bf16, st);

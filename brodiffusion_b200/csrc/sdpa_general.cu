@@ -78,8 +78,8 @@ __global__ void __launch_bounds__(128) sdpa_general_kernel(const SdpaGeneralArgs
                 const long long vld = seg ? a.v_ld[1] : a.v_ld[0];
                 const long long kbs = seg ? a.k_bs[1] : a.k_bs[0];
                 const long long vbs = seg ? a.v_bs[1] : a.v_bs[0];
-                kvv = ld16<kBf16>(kp, batch * kbs + static_cast<long long>(rr) * kld + head * hd + d);
-                vvv = ld16<kBf16>(vp, batch * vbs + static_cast<long long>(rr) * vld + head * hd + d);
+                kvv = ld16<kBf16>(kp, batch * kbs + static_cast<long long>(rr) * kld + (head / a.kv_group) * hd + d);
+                vvv = ld16<kBf16>(vp, batch * vbs + static_cast<long long>(rr) * vld + (head / a.kv_group) * hd + d);
                 if (a.key_scale != nullptr) kvv *= __ldg(a.key_scale + kg);
                 if (a.val_scale != nullptr) vvv *= __ldg(a.val_scale + kg);
             }

@@ -19,6 +19,7 @@ struct SdpaDevArgs {
     int mask_mode;
     int q_offset;   // Lk - Lq
     int hd_out;     // columns stored per head
+    int kv_group;   // query heads per K/V head (grouped-query attention), >= 1
     const float* key_mask;
     const float* key_scale;
     const float* val_scale;
@@ -65,6 +66,7 @@ struct SdpaGeneralArgs {
     int mask_mode;
     int q_offset;
     int head_dim;
+    int kv_group;   // query heads per K/V head, >= 1
     const float* key_mask;
     const float* key_scale;
     const float* val_scale;
@@ -177,6 +179,8 @@ cudaError_t launch_gemm(const GemmLaunch& L, cudaStream_t stream);
 
 // Elementwise helpers.
 cudaError_t launch_add_inplace(void* y, const void* x, long long n, bool bf16, cudaStream_t stream);
+cudaError_t launch_axpby_inplace(void* y, const void* x, long long n, float a, float b, bool bf16,
+                                 cudaStream_t stream);
 cudaError_t launch_add_row_bias(void* y, const void* bias, long long rows, long long cols, long long ld,
                                 bool bf16, cudaStream_t stream);
 cudaError_t launch_pad_heads(const void* src, void* dst, int rows, int num_heads, int hd, int hd_pad,

@@ -522,11 +522,12 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                         if (!ok) break;
                     }
                     const TileInfo ti = kv_tile(a, i >> 1);
+                    const int kv_head = head / a.kv_group;
                     const CUtensorMap* m = (i & 1) ? (ti.seg ? &tmV1 : &tmV0) : (ti.seg ? &tmK1 : &tmK0);
                     mbar_arrive_expect_tx(&kv_full[slot], C::kTileBytes);
                     for (int c = 0; c < C::kChunks; ++c) {
                         tma_load_4d(smem_kv + slot * C::kTileBytes + c * kChunkBytes, m, &kv_full[slot],
-                                    c * 64, head, ti.row0, batch);
+                                    c * 64, kv_head, ti.row0, batch);
                     }
                     issued = i + 1;
                 }

@@ -117,6 +117,12 @@ typedef struct bdattn_sdpa_params {
     const float* key_scale;      /* Lk floats or NULL */
     const float* val_scale;      /* Lk floats or NULL */
     float softmax_scale;         /* 0 => 1/sqrt(head_dim) */
+    /* Grouped-query attention (dit::gqa_attention_masked, src/dit/common.cpp:331-377):
+     * K and V carry num_kv_heads heads (k_ld/v_ld >= num_kv_heads*head_dim) and
+     * query head h reads K/V head h / (num_heads / num_kv_heads), so the widened
+     * Krep / Vrep copies of the reference (common.cpp:361-375) are never made.
+     * 0 or num_heads = plain multi-head attention; must divide num_heads. */
+    int num_kv_heads;
 } bdattn_sdpa_params;
 
 int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
@@ -426,6 +432,16 @@ int bdattn_add_inplace(void* y, const void* x, long long n, int dtype, bdattn_st
 
 int bdattn_add_row_bias(void* y, const void* bias, int rows, int cols, long long ld, int dtype,
                         bdattn_stream_t stream);
+
+/* Y = a*Y + b*X over n dense elements, in place: the device side of the
+ * prefix KV cache operations QwenImage21PrefixCache::scale_kv (brotensor
+ * scale_inplace, x = NULL and b = 0) and ::blend_from (brotensor axpby_inplace
+ * with a = 1 - alpha, b = alpha) of src/dit/qwenimage21_hooks.cpp:79-124, one
+ * call per cached K or V tensor.  Products and sum are rounded to FP32
+ * separately, the result once to the storage type.  Asynchronous on the
+ * stream (the reference follows the loop with sync_all; the caller syncs). */
+int bdattn_axpby_inplace(void* y, const void* x, long long n, float a, float b, int dtype,
+                         bdattn_stream_t stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -49,4 +49,37 @@ inline void joint_attention(const bt::Tensor& Q, const bt::Tensor& K, const bt::
     bt::flash_attention_forward(Qr, Kr, V, /*d_mask=*/nullptr, num_heads, /*causal=*/false, out);
 }
 
+// src/dit/common.cpp:331-377 (Krea 2): grouped-query heads, optional RoPE,
+// optional key mask.  The kernel reads K/V head h / group for query head h, so
+// the widened copies the reference materialises (Krep / Vrep, common.cpp:361-375)
+// are not made; the two scratch arguments are kept for source compatibility and
+// left untouched.
+inline void gqa_attention_masked(const bt::Tensor& Q, const bt::Tensor& K, const bt::Tensor& V,
+                                 const bt::Tensor* cos, const bt::Tensor* sin, int head_dim, int num_q_heads,
+                                 int num_kv_heads, const float* d_mask, bt::Tensor& out, bt::Tensor& Qr,
+                                 bt::Tensor& Kr, bt::Tensor& /*Krep*/, bt::Tensor& /*Vrep*/) {
+    if (num_q_heads <= 0 || num_kv_heads <= 0 || num_q_heads % num_kv_heads != 0)
+        throw std::runtime_error("gqa_attention_masked: num_kv_heads must divide num_q_heads");
+    if (head_dim <= 0 || Q.cols != head_dim * num_q_heads || K.cols != head_dim * num_kv_heads ||
+        V.cols != K.cols || K.rows != V.rows)
+        throw std::runtime_error("gqa_attention_masked: Q/K/V shapes do not agree with the head counts");
+    const bt::Tensor* Qp = &Q;
+    const bt::Tensor* Kp = &K;
+    if (cos != nullptr && sin != nullptr) {
+        bt::rope_apply(Q, *cos, *sin, head_dim, num_q_heads, Qr);
+        bt::rope_apply(K, *cos, *sin, head_dim, num_kv_heads, Kr);
+        Qp = &Qr;
+        Kp = &Kr;
+    }
+    out.resize(Q.rows, Q.cols, Q.dtype);
+    bdattn_sdpa_params p{};
+    p.dtype = bt::detail::bd_dtype(Q.dtype);
+    p.batch = 1; p.num_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
+    p.n_q_seg = 1; p.q[0] = Qp->data; p.o[0] = out.data; p.q_rows[0] = Q.rows; p.q_ld[0] = Q.cols; p.o_ld[0] = out.cols;
+    p.n_kv_seg = 1; p.k[0] = Kp->data; p.v[0] = V.data; p.kv_rows[0] = K.rows; p.k_ld[0] = K.cols; p.v_ld[0] = V.cols;
+    p.mask_mode = BDATTN_MASK_NONE;
+    p.key_mask = d_mask;
+    bt::detail::bd_check(bdattn_sdpa_fwd(&p, bt::detail::bd_stream()));
+}
+
 }  // namespace brodiffusion::dit

@@ -132,4 +132,19 @@ inline void flash_attention_project_kv(const Tensor& ctx, const Tensor& Wk, cons
                                        detail::bd_dtype(ctx.dtype), detail::bd_stream()));
 }
 
+// src/dit/qwenimage21_hooks.cpp:91-96 (QwenImage21PrefixCache::scale_kv)
+inline void scale_inplace(Tensor& Y, float a) {
+    detail::require_gpu(Y, "scale_inplace");
+    detail::bd_check(bdattn_axpby_inplace(Y.data, nullptr, static_cast<long long>(Y.size()), a, 0.0f,
+                                          detail::bd_dtype(Y.dtype), detail::bd_stream()));
+}
+// src/dit/qwenimage21_hooks.cpp:117-122 (QwenImage21PrefixCache::blend_from): y = a*y + b*x
+inline void axpby_inplace(Tensor& Y, const Tensor& X, float a, float b) {
+    detail::require_gpu(Y, "axpby_inplace");
+    if (Y.rows != X.rows || Y.cols != X.cols || Y.dtype != X.dtype)
+        throw std::runtime_error("axpby_inplace: Y and X must have the same shape and dtype");
+    detail::bd_check(bdattn_axpby_inplace(Y.data, X.data, static_cast<long long>(Y.size()), a, b,
+                                          detail::bd_dtype(Y.dtype), detail::bd_stream()));
+}
+
 }  // namespace brotensor

@@ -221,6 +221,38 @@ def joint_attention(Q, K, V, cos, sin, head_dim, num_heads, pair_mode=0, **kw):
     return sdpa(Qr, Kr, V, num_heads, **kw)
 
 
+def gqa_attention_masked(Q, K, V, cos, sin, head_dim, num_q_heads, num_kv_heads, key_mask=None, **kw):
+    """dit::gqa_attention_masked (src/dit/common.cpp:331-377): optional rope of Q
+    (num_q_heads) and K (num_kv_heads), then the K/V heads are widened so that
+    query head h reads K/V head h // group (common.cpp:361-375) and plain
+    attention runs on the widened tensors."""
+    if num_q_heads <= 0 or num_kv_heads <= 0 or num_q_heads % num_kv_heads:
+        raise ValueError("gqa_attention_masked: num_kv_heads must divide num_q_heads")
+    Qr, Kr = np.asarray(Q, np.float32), np.asarray(K, np.float32)
+    if cos is not None and sin is not None:
+        Qr = rope_apply(Qr, num_q_heads, head_dim, cos, sin)
+        Kr = rope_apply(Kr, num_kv_heads, head_dim, cos, sin)
+    group = num_q_heads // num_kv_heads
+    L = Kr.shape[0]
+    widen = lambda x: np.repeat(np.asarray(x, np.float32).reshape(L, num_kv_heads, head_dim), group, axis=1) \
+        .reshape(L, num_q_heads * head_dim)
+    return sdpa(Qr, widen(Kr), widen(V), num_q_heads, key_mask=key_mask, **kw)
+
+
+def prefix_cache_scale(t, scale, round_fn):
+    """QwenImage21PrefixCache::scale_kv on one cached tensor
+    (src/dit/qwenimage21_hooks.cpp:79-99): t *= scale, stored at the cache dtype
+    (round_fn rounds FP32 to that dtype)."""
+    return round_fn(np.float32(scale) * np.asarray(t, np.float32))
+
+
+def prefix_cache_blend(t, other, alpha, round_fn):
+    """QwenImage21PrefixCache::blend_from on one cached tensor
+    (src/dit/qwenimage21_hooks.cpp:101-124): t = (1 - alpha) * t + alpha * other."""
+    keep = np.float32(1.0) - np.float32(alpha)
+    return round_fn(keep * np.asarray(t, np.float32) + np.float32(alpha) * np.asarray(other, np.float32))
+
+
 def block_causal_tables(segments):
     """segments: list of ("text"|"image", n_tokens) incl. the target image last.
     Returns (seg_id per token, is_image per segment)."""

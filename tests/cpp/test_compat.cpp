@@ -95,6 +95,50 @@ static void test_joint_attention(int txt, int hp, int wp, int nh, int hd, const 
     expect_parity(label, ref, got, 0.0f, 1e-2f);
 }
 
+// dit::gqa_attention_masked (src/dit/common.cpp:331-377): the oracle widens the
+// K/V heads as the reference does and runs plain attention on the result.
+static void test_gqa(int L, int nq, int nkv, int hd, bool with_rope, bool with_mask, const char* label) {
+    const int Dq = nq * hd, Dkv = nkv * hd, group = nq / nkv;
+    const auto q = gen((std::size_t)L * Dq, 8101 + L, 1.0f, true), k = gen((std::size_t)L * Dkv, 8102 + L, 1.0f, true),
+               v = gen((std::size_t)L * Dkv, 8103 + L, 1.0f, true);
+    const std::vector<int> axes = hd == 128 ? std::vector<int>{16, 56, 56} : std::vector<int>{8, 28, 28};
+    std::vector<float> rcos((std::size_t)L * hd / 2), rsin(rcos.size());
+    // text rows rotate by the identity in the Flux tables; use image rows to exercise RoPE
+    bdo_flux_rope_tables(0, 1, L, hd, axes.data(), 3, 10000.f, rcos.data(), rsin.data());
+    std::vector<float> mask(L, 1.0f);
+    if (with_mask) for (int i = 0; i < L; i += 3) mask[i] = 0.0f;
+    std::vector<float> qr = q, kr = k;
+    if (with_rope) {
+        bdo_rope_apply(q.data(), L, nq, hd, rcos.data(), rsin.data(), 0, qr.data());
+        bdo_rope_apply(k.data(), L, nkv, hd, rcos.data(), rsin.data(), 0, kr.data());
+        for (auto& x : qr) x = bt::bf16_bits_to_fp32(bt::fp32_to_bf16_bits(x));
+        for (auto& x : kr) x = bt::bf16_bits_to_fp32(bt::fp32_to_bf16_bits(x));
+    }
+    std::vector<float> krep((std::size_t)L * Dq), vrep(krep.size()), ref(krep.size());
+    for (int r = 0; r < L; ++r)
+        for (int h = 0; h < nq; ++h)
+            for (int d = 0; d < hd; ++d) {
+                krep[(std::size_t)r * Dq + h * hd + d] = kr[(std::size_t)r * Dkv + (h / group) * hd + d];
+                vrep[(std::size_t)r * Dq + h * hd + d] = v[(std::size_t)r * Dkv + (h / group) * hd + d];
+            }
+    bdo_sdpa(qr.data(), L, krep.data(), vrep.data(), L, nq, hd, 0, nullptr, nullptr,
+             with_mask ? mask.data() : nullptr, nullptr, 0, 0, nullptr, L, 1, 0, ref.data(), nullptr);
+
+    bt::Tensor Q = gpu_t(q, L, Dq, bt::Dtype::BF16), K = gpu_t(k, L, Dkv, bt::Dtype::BF16),
+               V = gpu_t(v, L, Dkv, bt::Dtype::BF16);
+    bd::dit::RopeTables tab = bd::dit::build_axial_rope_tables(0, 1, L, hd, axes);
+    float* d_mask = nullptr;
+    CHECK(cudaMalloc(&d_mask, sizeof(float) * L) == cudaSuccess);
+    CHECK(cudaMemcpy(d_mask, mask.data(), sizeof(float) * L, cudaMemcpyHostToDevice) == cudaSuccess);
+    bt::Tensor out, Qr, Kr, Krep, Vrep;
+    bd::dit::gqa_attention_masked(Q, K, V, with_rope ? &tab.cos : nullptr, with_rope ? &tab.sin : nullptr, hd, nq, nkv,
+                                  with_mask ? d_mask : nullptr, out, Qr, Kr, Krep, Vrep);
+    bt::sync_all();
+    CHECK(Krep.data == nullptr && Vrep.data == nullptr);   // no widened copies
+    expect_parity(label, ref, download(out), 0.0f, 1e-2f);
+    cudaFree(d_mask);
+}
+
 static void test_geglu(int B, int D_in, int D_out, const char* label) {
     const auto x = gen((std::size_t)B * D_in, 21, 1.0f, false), w = gen((std::size_t)2 * D_out * D_in, 22, 0.1f, false),
                b = gen((std::size_t)2 * D_out, 23, 0.2f, false);
@@ -176,6 +220,8 @@ int main() {
         std::printf("test_compat: host mirror over libbdattn\n");
         test_joint_attention(3, 4, 4, 2, 8, {2, 2, 4}, "joint_attention tiny (2x8)");       // tests/test_flux_blocks.cpp:480-507
         test_joint_attention(40, 16, 16, 4, 128, {16, 56, 56}, "joint_attention 4x128");
+        test_gqa(200, 8, 2, 128, true, true, "gqa 8q/2kv x128 rope+mask");
+        test_gqa(150, 6, 3, 64, false, false, "gqa 6q/3kv x64");
         test_geglu(40, 64, 48, "geglu B40 64->48");
         test_geglu(128, 128, 96, "geglu B128 128->96");
         test_adds();

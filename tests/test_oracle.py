@@ -189,3 +189,21 @@ def test_oracle_matches_torch_sdpa(oracle):
     ref = torch.nn.functional.scaled_dot_product_attention(tq, tk, tv)
     ref = ref.transpose(0, 1).reshape(L, -1).numpy()
     assert np.abs(oracle.sdpa(q, k, v, nh) - ref).max() < 2e-6
+
+
+def test_gqa_matches_torch_grouped_attention(oracle):
+    """dit::gqa_attention_masked restated (K/V heads widened, then plain
+    attention) against PyTorch's FP32 grouped-query attention."""
+    import torch
+    rng = np.random.default_rng(12)
+    L, nq, nkv, hd = 70, 6, 2, 24
+    q = rng.standard_normal((L, nq * hd)).astype(np.float32)
+    k, v = (rng.standard_normal((L, nkv * hd)).astype(np.float32) for _ in range(2))
+    tq = torch.from_numpy(q).view(L, nq, hd).transpose(0, 1)
+    tk, tv = (torch.from_numpy(a).view(L, nkv, hd).transpose(0, 1) for a in (k, v))
+    ref = torch.nn.functional.scaled_dot_product_attention(tq, tk, tv, enable_gqa=True)
+    ref = ref.transpose(0, 1).reshape(L, -1).numpy()
+    got = oracle.gqa_attention_masked(q, k, v, None, None, hd, nq, nkv)
+    assert np.abs(got - ref).max() < 2e-6
+    with pytest.raises(ValueError):
+        oracle.gqa_attention_masked(q, k, v, None, None, hd, nq, 4)

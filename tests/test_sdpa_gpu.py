@@ -251,6 +251,37 @@ def test_sana_and_pixart_cross_attention_head_dims(bd, oracle):
         G.check(out[rows], oracle.sdpa(q, k, v, nh, key_mask=km, rows=rows), what=f"hd={hd} masked cross-attn")
 
 
+@pytest.mark.parametrize("nq,nkv,hd", [(8, 2, 128), (6, 3, 64), (4, 1, 80), (4, 2, 160)])
+def test_grouped_query_heads_without_widening(bd, oracle, nq, nkv, hd):
+    """Krea 2 attention (dit::gqa_attention_masked, src/dit/common.cpp:331-377):
+    K/V carry nkv heads and the kernel maps query head h to K/V head h // group;
+    the oracle widens K/V as the reference does.  Key mask as in the text-fusion
+    call, ragged length, both kernels (hd 160 takes the general one)."""
+    L = 333
+    q = synth.activations((L, nq * hd), 9700 + hd)
+    k = synth.activations((L, nkv * hd), 9701 + hd)
+    v = synth.activations((L, nkv * hd), 9702 + hd)
+    km = np.ones(L, np.float32); km[::5] = 0.0
+    for mask in (None, km):
+        out = G.sdpa(bd, q, k, v, nq, num_kv_heads=nkv, key_mask=None if mask is None else mask.copy())
+        ref = oracle.gqa_attention_masked(q, k, v, None, None, hd, nq, nkv, key_mask=mask)
+        G.check(out, ref, what=f"gqa {nq}/{nkv} x{hd} mask={mask is not None}")
+    # equal head counts are plain multi-head attention
+    out = G.sdpa(bd, q, synth.activations((L, nq * hd), 9703), synth.activations((L, nq * hd), 9704), nq, num_kv_heads=nq)
+    ref = oracle.sdpa(q, synth.activations((L, nq * hd), 9703), synth.activations((L, nq * hd), 9704), nq)
+    G.check(out, ref, what="gqa with equal head counts")
+
+
+def test_grouped_query_heads_refusals(bd):
+    q = torch.zeros(64, 8 * 64, device="cuda", dtype=torch.bfloat16)
+    kv = torch.zeros(64, 3 * 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(bd.BdattnError, match="num_kv_heads must divide num_heads"):
+        bd.sdpa_fwd(q, kv, kv, torch.empty_like(q), 8, num_kv_heads=3)
+    kv2 = torch.zeros(64, 2 * 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(bd.BdattnError, match="smaller than num_kv_heads"):
+        bd.sdpa_fwd(q, kv2, kv2, torch.empty_like(q), 8, num_kv_heads=4)
+
+
 # --------------------------------------------------------------- edge cases
 @pytest.mark.parametrize("hd", [128, 64, 40, 72, 112, 160])
 @pytest.mark.parametrize("L", [1, 63, 64, 65, 127, 129, 257])
