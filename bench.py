@@ -2,7 +2,7 @@
 """Benchmark of the denoiser-attention hot path.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                  [--workload flux1024|flux2048_headsharded]
+                  [--workload flux1024|flux2048_headsharded|sana1024|sana4096|flux1024_qkv_proj|flux1024_out_proj]
 
 One step = one pass of the hot path over one synthetic batch:
   flux1024              (1 GPU)  Flux.1 joint attention at 1024 px, double-stream
@@ -12,6 +12,9 @@ One step = one pass of the hot path over one synthetic batch:
   flux2048_headsharded  (N GPUs) Flux.1 joint attention at 2048 px, batch 2,
                         512 + 16384 tokens; heads split over the ranks, NCCL
                         all-gather of the per-head outputs.  Default for N > 1.
+  sana1024 / sana4096   (1 GPU)  Sana ReLU linear attention, batch 2 (GB/s).
+  flux1024_qkv_proj / flux1024_out_proj  (1 GPU)  the projections either side of
+                        the flux1024 attention call (projection TFLOP/s).
 The metric is attention TFLOP/s with the reference's own FLOP convention
 (4 * Lq * Lk * heads * head_dim, tools/bench_krea2_kernels.cpp:188-192).
 
@@ -428,6 +431,80 @@ def run_sana(args):
     print(json.dumps(line), flush=True)
 
 
+PROJ_WORKLOADS = {"flux1024_qkv_proj": 3, "flux1024_out_proj": 1}
+
+
+def run_proj(args):
+    """Projections around the Flux 1024 px attention call on one GPU
+    (4608 tokens, 3072 -> 3072 features, BF16): flux1024_qkv_proj = one
+    bdattn_qkv_norm_rope_fwd call (Q, K and V projections with per-head RMSNorm
+    and RoPE in the epilogue), flux1024_out_proj = one bdattn_linear_fwd call.
+    metric = projection TFLOP/s (2 * tokens * in * out per projection).  Steps
+    are replayed from a CUDA graph; activations rotate over sets larger than L2."""
+    import torch
+    import brodiffusion_b200 as bd
+    torch.cuda.set_device(0)
+    n_proj = PROJ_WORKLOADS[args.workload]
+    L, Dm, nh, hd = 4608, 3072, 24, 128
+    gen = torch.Generator(device="cuda").manual_seed(9876)
+    n_sets = 6                                   # 6 x 28 MB of activations > 126 MB L2
+    xs = [torch.randn(L, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(n_sets)]
+    W = [torch.randn(Dm, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) * 0.02 for _ in range(n_proj)]
+    outs = [torch.empty(L, Dm, device="cuda", dtype=torch.bfloat16) for _ in range(n_proj)]
+    gain = torch.ones(hd, device="cuda", dtype=torch.bfloat16)
+    cos, sin = bd.rope_tables_flux(512, 64, 64, hd)
+
+    def step(i):
+        x = xs[i % n_sets]
+        if n_proj == 3:
+            bd.qkv_norm_rope_fwd(x, W[0], W[1], W[2], outs[0], outs[1], outs[2], nh, hd, gain_q=gain, gain_k=gain,
+                                 cos=cos, sin=sin)
+        else:
+            bd.linear_fwd(x, W[0], None, outs[0])
+
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(args.steps):
+                step(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler.start()
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    t_end = time.perf_counter() + 0.3
+    while time.perf_counter() < t_end:
+        graph.replay()
+    torch.cuda.synchronize()
+    sampler.stop()
+    if bd.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure")
+    peak_tf, _, kind = measured_peaks()
+    tf = n_proj * 2.0 * L * Dm * Dm / (ms * 1e-3) / 1e12
+    line = {"metric": "projection TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens": L, "in_features": Dm, "out_features": Dm,
+                       "projections": n_proj, "heads": nh, "head_dim": hd,
+                       "l2": f"rotating {n_sets} activation sets ({n_sets * L * Dm * 2 / 1e6:.0f} MB > 126 MB L2)",
+                       "timing": "CUDA-graph replay of the steps"},
+            "clocks": sampler.summary(), "gpu_launches": args.steps,
+            "roofline": {"bound": "tensor", "kernel": "gemm_wide_kernel", "achieved": tf, "peak": peak_tf,
+                         "unit": "TFLOP/s", "frac": tf / peak_tf, "peak_kind": f"{kind} cuBLAS BF16 burst",
+                         "traffic": None}}
+    print(json.dumps(line), flush=True)
+
+
 def cpu_baseline(L):
     """Oracle port of the reference attention core on the host cores, on a
     bounded sample of the same workload (about 10-20 s of CPU work)."""
@@ -460,7 +537,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(SANA_WORKLOADS), default=None)
+    ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(SANA_WORKLOADS) + sorted(PROJ_WORKLOADS),
+                    default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
@@ -475,6 +553,11 @@ def main():
         if args.impl == "reference" or world > 1:
             raise SystemExit("the sana workloads run on one GPU with --impl ours")
         run_sana(args)
+        return
+    if args.workload in PROJ_WORKLOADS:
+        if args.impl == "reference" or world > 1:
+            raise SystemExit("the projection workloads run on one GPU with --impl ours")
+        run_proj(args)
         return
     if args.impl == "reference":
         run_reference(args, rank, world)
