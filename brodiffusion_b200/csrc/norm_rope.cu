@@ -161,9 +161,10 @@ __global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a
         for (int it = 0; it < kUnroll; ++it) {
             const long long u = base + it * kUnitsPerWarp + sub;
             live[it] = u < n_units;
-            const long long uu = live[it] ? u : 0;
-            const int row = static_cast<int>(uu / a.num_heads);
-            const int head = static_cast<int>(uu - static_cast<long long>(row) * a.num_heads);
+            // 32-bit division: a job has fewer than 2^31 (token, head) units (checked at launch)
+            const unsigned uu = live[it] ? static_cast<unsigned>(u) : 0u;
+            const int row = static_cast<int>(uu / static_cast<unsigned>(a.num_heads));
+            const int head = static_cast<int>(uu - static_cast<unsigned>(row) * static_cast<unsigned>(a.num_heads));
             const long long xoff = static_cast<long long>(row) * job.x_ld + head * hd + l * 8;
             ooff[it] = static_cast<long long>(row) * job.out_ld + head * hd + l * 8;
             v[it] = live[it] ? *reinterpret_cast<const uint4*>(xin + xoff) : make_uint4(0, 0, 0, 0);
@@ -240,7 +241,8 @@ cudaError_t launch_norm_rope(const NormRopeArgs& a, bool bf16, cudaStream_t stre
     // Vector path when every job is 16-byte aligned and the head is a
     // power-of-two number of 8-element slots.
     const int hd = a.head_dim;
-    bool vec = a.pair_mode == 0 && hd % 8 == 0 && ((hd / 8) & (hd / 8 - 1)) == 0 && hd <= 256;
+    bool vec = a.pair_mode == 0 && hd % 8 == 0 && ((hd / 8) & (hd / 8 - 1)) == 0 && hd <= 256 &&
+               max_units < (1LL << 31);
     for (int i = 0; i < a.n_jobs && vec; ++i) {
         const NormRopeJobDev& j = a.job[i];
         if ((reinterpret_cast<uintptr_t>(j.x) & 15u) || (reinterpret_cast<uintptr_t>(j.out) & 15u) ||
