@@ -209,7 +209,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1);
-            mbar_init(&p_full[t], kBM);
+            mbar_init(&p_full[t], 4);          // one arrival per softmax warp of the tile
             mbar_init(&pv_done[t], 1);
         }
         fence_mbar_init();
@@ -362,7 +362,10 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             l_sum += ((rs[0] + rs[1]) + (rs[2] + rs[3])) + ((rs[4] + rs[5]) + (rs[6] + rs[7]));
             tmem_wait_st();
             tc_fence_before();
-            mbar_arrive(&p_full[t]);
+            // one elected arrival per warp: 32 lanes arriving on the same barrier
+            // word serialise and delay the hand-over to the MMA warp
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[t]);
         }
 
         if (ok && n_kv > 0) {
@@ -433,6 +436,14 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         setmaxnreg_dec<kRegsOther>();
         if (warp == 8) {
             // -------------------------------------------------- MMA issuer
+            // tcgen05.mma issue blocks while the pipe is busy, and everything this
+            // warp does between two batches of MMAs (barrier waits, commits, index
+            // arithmetic) is time the tensor pipe idles, so the loop is kept short:
+            // ring slots and phases are walked without divisions, the K/V waits sit
+            // before the wait for P, and descriptors are formed from per-tile bases.
+            // (Two issuing warps, one per query tile, were slower: MMAs of the two
+            // tiles then interleave in the pipe and lose their back-to-back runs on
+            // one accumulator.)
             constexpr int kFmt = kBf16 ? 1 : 0;
             constexpr uint32_t idesc_qk = make_idesc_f16(kFmt, kBM, kBN, 0, 0);
             constexpr uint32_t idesc_pv = make_idesc_f16(kFmt, kBM, HD, 0, 1);
@@ -473,34 +484,43 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 }
                 __syncwarp();
             }
+            // slot and phase of the V tile of step j (ring item 2j+1) and of the K tile
+            // of step j+1 (item 2j+2)
+            int vslot = 1 % ST, vphase = 0;
             for (int j = 0; ok && j < n_kv; ++j) {
-                const int iv = 2 * j + 1;
-                const int vslot = iv % ST;
-                ok = mbar_wait(&kv_full[vslot], static_cast<uint32_t>((iv / ST) & 1));
+                int kslot = vslot + 1, kphase = vphase;
+                if (kslot == ST) { kslot = 0; kphase ^= 1; }
+                const bool more = j + 1 < n_kv;
+                ok = mbar_wait(&kv_full[vslot], static_cast<uint32_t>(vphase));
+                if (ok && more) ok = mbar_wait(&kv_full[kslot], static_cast<uint32_t>(kphase));
+                if (ok) ok = mbar_wait(&p_full[0], static_cast<uint32_t>(j & 1));
                 if (!ok) break;
-                const int ik = 2 * j + 2;
-                const int kslot = ik % ST;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    ok = mbar_wait(&p_full[t], static_cast<uint32_t>(j & 1));
-                    if (!ok) break;
-                    if (t == 0 && j + 1 < n_kv) {
-                        ok = mbar_wait(&kv_full[kslot], static_cast<uint32_t>((ik / ST) & 1));
-                        if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    issue_pv(0, vslot, j > 0);
+                    umma_commit(&pv_done[0]);
+                    if (more) {
+                        issue_qk(0, kslot);
+                        umma_commit(&s_full[0]);
                     }
-                    tc_fence_after();
-                    if (lane == 0) {
-                        issue_pv(t, vslot, j > 0);
-                        umma_commit(&pv_done[t]);
-                        if (j + 1 < n_kv) {
-                            issue_qk(t, kslot);
-                            umma_commit(&s_full[t]);
-                            if (t == 1) umma_commit(&kv_empty[kslot]);
-                        }
-                    }
-                    __syncwarp();
                 }
-                if (ok && lane == 0) umma_commit(&kv_empty[vslot]);
                 __syncwarp();
+                ok = mbar_wait(&p_full[1], static_cast<uint32_t>(j & 1));
+                if (!ok) break;
+                tc_fence_after();
+                if (lane == 0) {
+                    issue_pv(1, vslot, j > 0);
+                    umma_commit(&pv_done[1]);
+                    umma_commit(&kv_empty[vslot]);
+                    if (more) {
+                        issue_qk(1, kslot);
+                        umma_commit(&s_full[1]);
+                        umma_commit(&kv_empty[kslot]);
+                    }
+                }
+                __syncwarp();
+                vslot = kslot + 1; vphase = kphase;
+                if (vslot == ST) { vslot = 0; vphase ^= 1; }
             }
         } else if (warp == 9) {
             // ------------------------------------------------ TMA producer

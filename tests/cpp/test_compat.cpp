@@ -169,6 +169,24 @@ static void test_adds() {
     }
 }
 
+// QwenImage21PrefixCache::scale_kv / blend_from on one cached tensor
+// (src/dit/qwenimage21_hooks.cpp:79-124): scale_inplace, then axpby_inplace.
+static void test_prefix_cache_ops() {
+    const int rows = 256, cols = 96;
+    const auto y0 = gen((std::size_t)rows * cols, 61, 1.0f, true), x = gen(y0.size(), 62, 1.0f, true);
+    bt::Tensor Y = gpu_t(y0, rows, cols, bt::Dtype::BF16), X = gpu_t(x, rows, cols, bt::Dtype::BF16);
+    bt::scale_inplace(Y, 0.75f);
+    bt::axpby_inplace(Y, X, 1.0f - 0.3f, 0.3f);
+    std::vector<float> ref(y0.size());
+    for (std::size_t i = 0; i < ref.size(); ++i) {
+        const float s = bt::bf16_bits_to_fp32(bt::fp32_to_bf16_bits(0.75f * y0[i]));
+        const volatile float p1 = (1.0f - 0.3f) * s, p2 = 0.3f * x[i];   // no contraction into an FMA
+        ref[i] = bt::bf16_bits_to_fp32(bt::fp32_to_bf16_bits(p1 + p2));
+    }
+    const auto got = download(Y);
+    CHECK(got == ref);   // products and sum rounded separately: bit-exact
+}
+
 static void test_unet_attention() {
     // SD1.5-shaped block, smaller token count: (512, 320), 8 heads x 40, ctx (77, 768)
     const int L = 512, C = 320, nh = 8, Lc = 77, Cc = 768;
@@ -225,6 +243,7 @@ int main() {
         test_geglu(40, 64, 48, "geglu B40 64->48");
         test_geglu(128, 128, 96, "geglu B128 128->96");
         test_adds();
+        test_prefix_cache_ops();
         test_unet_attention();
         test_refusals();
         int status = 0;
