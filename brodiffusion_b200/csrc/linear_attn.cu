@@ -14,9 +14,9 @@
 //           fragments in registers, z summed from the same fragments;
 //   reduce  warps -> CTA in shared memory, CTA -> cluster through distributed
 //           shared memory (no global scratch);
-//   pass B  Q chunks -> out = [S; z] relu(Q) with the FP32 state split into
-//           BF16 high and low parts (two MMAs) so the state keeps ~16 bits,
-//           division by the z row, BF16 store through a staging tile.
+//   pass B  Q chunks -> out = [S; z] relu(Q) with the state rounded to BF16
+//           (FP32 accumulation), division by the z row, BF16 store through a
+//           staging tile.
 // Tiles arrive by TMA (64-token x 32-row boxes, 128-byte swizzle) into a ring
 // shared by both passes and fed by a dedicated producer warp (full / empty
 // mbarriers, no CTA-wide barrier in the loops), so the first Q chunks are in
@@ -91,6 +91,13 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                             ~static_cast<uintptr_t>(1023));
     cg::cluster_group cluster = cg::this_cluster();
     const int cs = static_cast<int>(cluster.num_blocks());
+    // Phase barrier of everything that shares this (batch, head): the cluster
+    // barrier, or, for a cluster of one CTA, a plain block barrier (the hardware
+    // cluster barrier costs microseconds even when it has a single member).
+    auto phase_sync = [&]() {
+        if (cs == 1) __syncthreads();
+        else cluster.sync();
+    };
     const int rank = static_cast<int>(cluster.block_rank());
     const int head = blockIdx.y;
     const int batch = blockIdx.z;
@@ -152,8 +159,8 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int it = 0; it < first && ok; ++it) { issue(it); if (ok) issued = it + 1; }
         }
         __syncwarp();
-        cluster.sync();
-        cluster.sync();
+        phase_sync();
+        phase_sync();
         if (lane == 0) {
             for (int it = first; it < n_items && ok; ++it) { issue(it); if (ok) issued = it + 1; }
             if (!ok) {
@@ -163,7 +170,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             }
         }
         __syncwarp();
-        cluster.sync();
+        phase_sync();
         return;
     }
 
@@ -243,7 +250,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int w = 0; w < kLaWarps; ++w) s += sm.partial[w][i];
         sm.local_state[i] = s;
     }
-    cluster.sync();
+    phase_sync();
     for (int i = tid; i < kLaState; i += kLaWarps * 32) {
         float s = 0.0f;
         for (int r = 0; r < cs; ++r) {
@@ -255,10 +262,15 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
         sm.state[i] = s;
     }
-    cluster.sync();
+    phase_sync();
 
-    // pass B: A fragments of [S; z] (48 x 32, rows 33.. zero), split hi + lo
-    uint32_t ah[3][2][4], al[3][2][4];
+    // pass B: A fragments of [S; z] (48 x 32, rows 33.. zero) rounded to BF16.
+    // The output is rounded to BF16 anyway (2^-9 relative per element); rounding
+    // the 32 state terms of a dot product adds about 2^-9 / sqrt(32) to that, and
+    // the reference's own batched path keeps S and z in BF16 (src/dit/sana.cpp:538-546).
+    // A second MMA with the rounding residue doubled the work of this pass, which
+    // is bound by the legacy tensor path (one m16n8k16 per 16 cycles and scheduler).
+    uint32_t ah[3][2][4];
 #pragma unroll
     for (int mt = 0; mt < 3; ++mt)
 #pragma unroll
@@ -269,10 +281,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 const int col = ks * 16 + q4 * 2 + (r >> 1) * 8;
                 const float x0 = sm.state[row * 32 + col];
                 const float x1 = sm.state[row * 32 + col + 1];
-                const float h0 = __bfloat162float(__float2bfloat16_rn(x0));
-                const float h1 = __bfloat162float(__float2bfloat16_rn(x1));
-                ah[mt][ks][r] = pack2<true>(h0, h1);
-                al[mt][ks][r] = pack2<true>(x0 - h0, x1 - h1);
+                ah[mt][ks][r] = pack2<true>(x0, x1);
             }
 
     for (int it = n_mine; it < n_items; ++it) {
@@ -299,8 +308,6 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
                         for (int ks = 0; ks < 2; ++ks) {
                             mma_bf16(o[mt], ah[mt][ks][0], ah[mt][ks][1], ah[mt][ks][2], ah[mt][ks][3],
-                                     b[2 * ks], b[2 * ks + 1]);
-                            mma_bf16(o[mt], al[mt][ks][0], al[mt][ks][1], al[mt][ks][2], al[mt][ks][3],
                                      b[2 * ks], b[2 * ks + 1]);
                         }
                     }
@@ -342,7 +349,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty[slot]);
     }
-    cluster.sync();
+    phase_sync();
 }
 
 }  // namespace
