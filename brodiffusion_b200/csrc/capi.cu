@@ -609,7 +609,8 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     a.ld = ld; a.batch_stride = batch_stride > 0 ? batch_stride : static_cast<long long>(num_heads) * 32 * ld;
     a.eps = eps; a.sz_in = sz_in; a.w_in = w_in; a.sz_out = sz_out;
     const long long D = static_cast<long long>(num_heads) * 32;
-    CUtensorMap tq, tk, tv;
+    CUtensorMap tq, tk, tv, to;
+    if (make_map_3d(op, &to, out, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tq, q, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tk, k, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tv, v, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
@@ -618,7 +619,15 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     const int chunks = (n_tokens + 127) / 128;
     int cs = 1;
     while (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 148 && chunks >= cs * 2) cs *= 2;
-    cudaError_t e = bdattn::launch_linear_attn(a, tq, tk, tv, cs, reinterpret_cast<cudaStream_t>(stream));
+    // Long sequences: split once more and let two CTAs share an SM (three ring
+    // items each instead of eight), so that one CTA's reduction and barriers hide
+    // behind the other's streaming.  Not worth a cluster barrier on short ones.
+    a.stages = 8;
+    if (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 296 && chunks >= cs * 2 * 8) {
+        cs *= 2;
+        a.stages = 3;
+    }
+    cudaError_t e = bdattn::launch_linear_attn(a, tq, tk, tv, to, cs, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
 }

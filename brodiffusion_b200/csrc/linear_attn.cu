@@ -15,8 +15,8 @@
 //   reduce  warps -> CTA in shared memory, CTA -> cluster through distributed
 //           shared memory (no global scratch);
 //   pass B  Q chunks -> out = [S; z] relu(Q) with the state rounded to BF16
-//           (FP32 accumulation), division by the z row, BF16 store through a
-//           staging tile.
+//           (FP32 accumulation), division by the z row, BF16 tile staged in
+//           shared memory and written by TMA store.
 // Tiles arrive by TMA (64-token x 32-row boxes, 128-byte swizzle) into a ring
 // shared by both passes and fed by a dedicated producer warp (full / empty
 // mbarriers, no CTA-wide barrier in the loops), so the first Q chunks are in
@@ -34,20 +34,19 @@ namespace cg = cooperative_groups;
 constexpr int kLaWarps = 8;                   // consumer warps; one more warp feeds the ring by TMA
 constexpr int kLaThreads = (kLaWarps + 1) * 32;
 constexpr int kLaChunk = 128;                 // tokens per ring item
-constexpr int kLaStages = 8;                  // 8 x 16 KB in flight per SM
+constexpr int kLaMaxStages = 8;               // ring of 16 KB items: 8 with one CTA per SM, 3 when two share it
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
 constexpr int kLaState = 33 * 32;             // [S; z] floats
-constexpr int kLaOutLd = 136;                 // staging row stride (elements)
 
 struct LaSmem {
-    alignas(1024) uint8_t ring[kLaStages][kLaSlotBytes];
     float partial[kLaWarps][kLaState];
     float local_state[kLaState];
     float state[48 * 32];   // rows 33..47 zero
-    alignas(16) __nv_bfloat16 out_stage[2][32 * kLaOutLd];
-    uint64_t full[kLaStages];
-    uint64_t empty[kLaStages];
+    alignas(1024) uint8_t out_stage[2][2 * kLaBoxBytes];   // two 32 x 128-token output tiles, box layout
+    uint64_t full[kLaMaxStages];
+    uint64_t empty[kLaMaxStages];
+    alignas(1024) uint8_t ring[1][kLaSlotBytes];   // a.stages items follow (dynamic shared memory)
 };
 
 __device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2,
@@ -83,9 +82,10 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(kLaThreads)
+__global__ void __launch_bounds__(kLaThreads, 2)
 linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                   const __grid_constant__ CUtensorMap tmV, const LinearAttnArgs a) {
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
+                   const LinearAttnArgs a) {
     extern __shared__ uint8_t la_raw[];
     LaSmem& sm = *reinterpret_cast<LaSmem*>((reinterpret_cast<uintptr_t>(la_raw) + 1023) &
                                             ~static_cast<uintptr_t>(1023));
@@ -115,6 +115,8 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int n_b = (n_mine + 1) / 2;  // pass B items carry two 128-token Q chunks (16 KB, like a pass A item)
     const int n_items = n_mine + n_b;  // pass A items (K + V chunks), then pass B items
     const int row0 = head * 32;
+    const int kLaStages = a.stages;
+    uint8_t* const ring_base = &sm.ring[0][0];     // a.stages items of kLaSlotBytes
 
     if (tid == 0) {
         for (int s = 0; s < kLaStages; ++s) {
@@ -135,7 +137,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 ok = mbar_wait(&sm.empty[slot], static_cast<uint32_t>(((item / kLaStages) - 1) & 1));
                 if (!ok) return;
             }
-            uint8_t* dst = sm.ring[slot];
+            uint8_t* dst = ring_base + slot * kLaSlotBytes;
             if (item < n_mine) {
                 const int tok = (c_begin + item) * kLaChunk;
                 mbar_arrive_expect_tx(&sm.full[slot], 4 * kLaBoxBytes);
@@ -194,7 +196,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
         if (ok) {
-            const uint32_t kb = smem_u32(sm.ring[slot]) + box * kLaBoxBytes;
+            const uint32_t kb = smem_u32(ring_base + slot * kLaSlotBytes) + box * kLaBoxBytes;
             const uint32_t vb = kb + 2 * kLaBoxBytes;
             uint32_t af[2][4];
 #pragma unroll
@@ -291,9 +293,9 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int sub = 0; sub < 2; ++sub) {
             const int cidx = 2 * (it - n_mine) + sub;     // 128-token chunk of this CTA
             if (cidx >= n_mine) break;
-            __nv_bfloat16* stage = sm.out_stage[cidx & 1];
+            uint8_t* stage = sm.out_stage[cidx & 1];
             if (ok) {
-                const uint32_t qb = smem_u32(sm.ring[slot]) + (2 * sub + box) * kLaBoxBytes;
+                const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (2 * sub + box) * kLaBoxBytes;
 #pragma unroll
                 for (int nt = 0; nt < 2; ++nt) {
                     uint32_t b[4];
@@ -316,47 +318,46 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
                     const float r0 = 1.0f / (den0 + a.eps);
                     const float r1 = 1.0f / (den1 + a.eps);
-                    const int tok = warp * 16 + nt * 8 + q4 * 2;
+                    // the tile is staged in the layout of two 64-token TMA boxes
+                    // (128-byte swizzle), which also keeps these writes conflict-free
+                    const int tok = (warp & 3) * 16 + nt * 8 + q4 * 2;      // inside the 64-token box
+                    uint8_t* sbox = stage + box * kLaBoxBytes + (tok & 7) * 2;
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
                         const int i0 = mt * 16 + g;
-                        *reinterpret_cast<uint32_t*>(&stage[i0 * kLaOutLd + tok]) =
-                            pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
-                        *reinterpret_cast<uint32_t*>(&stage[(i0 + 8) * kLaOutLd + tok]) =
-                            pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
+                        *reinterpret_cast<uint32_t*>(sbox + swz(i0, tok >> 3)) = pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
+                        *reinterpret_cast<uint32_t*>(sbox + swz(i0 + 8, tok >> 3)) = pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
                     }
                 }
             }
+            // The staged tile leaves by TMA (one thread, asynchronous), so the warps go
+            // straight on to the next chunk.  Before the barrier the issuing thread
+            // makes sure its earlier stores have finished reading shared memory: the
+            // buffer the next chunk is staged in was last read by the store of the
+            // chunk before this one.
+            fence_proxy_async_smem();
+            if (tid == 0) tma_store_wait_read_all();
             asm volatile("bar.sync 1, 256;" ::: "memory");   // the 32 x 128 output tile is complete
-            if (ok) {
+            if (ok && tid == 0) {
                 const int tok0 = (c_begin + cidx) * kLaChunk;
-#pragma unroll
-                for (int rep = 0; rep < 2; ++rep) {
-                    const int idx = tid + rep * kLaWarps * 32;
-                    const int row = idx >> 4;
-                    const int c16 = idx & 15;
-                    const int tok = tok0 + c16 * 8;
-                    if (tok < a.n_tokens) {
-                        const uint4 w = *reinterpret_cast<const uint4*>(&stage[row * kLaOutLd + c16 * 8]);
-                        __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.out) +
-                                             static_cast<long long>(batch) * a.batch_stride +
-                                             static_cast<long long>(row0 + row) * a.ld + tok;
-                        *reinterpret_cast<uint4*>(dst) = w;
-                    }
-                }
+                tma_store_3d(&tmO, stage, tok0, row0, batch);
+                if (tok0 + 64 < a.n_tokens) tma_store_3d(&tmO, stage + kLaBoxBytes, tok0 + 64, row0, batch);
+                tma_store_commit();
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty[slot]);
     }
+    if (tid == 0) tma_store_wait_all();     // shared memory stays valid until the last store has left
     phase_sync();
 }
 
 }  // namespace
 
 cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
-                               const CUtensorMap& tmV, int cluster_size, cudaStream_t stream) {
-    const size_t smem = sizeof(LaSmem) + 1024;
+                               const CUtensorMap& tmV, const CUtensorMap& tmO, int cluster_size,
+                               cudaStream_t stream) {
+    const size_t smem = sizeof(LaSmem) + static_cast<size_t>(a.stages - 1) * kLaSlotBytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(linear_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          static_cast<int>(smem));
     if (e != cudaSuccess) return e;
@@ -373,7 +374,7 @@ cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, linear_attn_kernel, tmQ, tmK, tmV, a);
+    return cudaLaunchKernelEx(&cfg, linear_attn_kernel, tmQ, tmK, tmV, tmO, a);
 }
 
 }  // namespace bdattn

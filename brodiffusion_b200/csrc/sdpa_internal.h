@@ -129,9 +129,11 @@ struct LinearAttnArgs {
     const float* sz_in;
     float w_in;
     float* sz_out;
+    int stages;   // ring items of 16 KB per CTA (3: two CTAs per SM, up to 8: one)
 };
 cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, const CUtensorMap& tmK,
-                               const CUtensorMap& tmV, int cluster_size, cudaStream_t stream);
+                               const CUtensorMap& tmV, const CUtensorMap& tmO, int cluster_size,
+                               cudaStream_t stream);
 
 // Linear layers (tcgen05 GEMM), up to three problems per launch.
 struct GemmProblem {
