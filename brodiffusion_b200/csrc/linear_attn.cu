@@ -253,16 +253,37 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         sm.local_state[i] = s;
     }
     phase_sync();
-    for (int i = tid; i < kLaState; i += kLaWarps * 32) {
-        float s = 0.0f;
-        for (int r = 0; r < cs; ++r) {
-            const float* remote = cluster.map_shared_rank(sm.local_state, r);
-            s += remote[i];
+    {
+        // every thread owns up to five state elements; all remote (distributed
+        // shared memory) loads are issued before the first add so that their
+        // latencies overlap
+        constexpr int kPer = (kLaState + kLaWarps * 32 - 1) / (kLaWarps * 32);
+        float part[kPer][8];
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) {
+            const int i = tid + e * kLaWarps * 32;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                part[e][r] = 0.0f;
+                if (r < cs && i < kLaState) {
+                    const float* remote = cs == 1 ? sm.local_state : cluster.map_shared_rank(sm.local_state, r);
+                    part[e][r] = remote[i];
+                }
+            }
         }
-        const long long so = (static_cast<long long>(batch) * a.num_heads + head) * kLaState + i;
-        if (a.sz_out != nullptr && rank == 0) a.sz_out[so] = s;
-        if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
-        sm.state[i] = s;
+#pragma unroll
+        for (int e = 0; e < kPer; ++e) {
+            const int i = tid + e * kLaWarps * 32;
+            if (i < kLaState) {
+                float s = 0.0f;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) s += part[e][r];      // rank order, as before
+                const long long so = (static_cast<long long>(batch) * a.num_heads + head) * kLaState + i;
+                if (a.sz_out != nullptr && rank == 0) a.sz_out[so] = s;
+                if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
+                sm.state[i] = s;
+            }
+        }
     }
     phase_sync();
 
