@@ -202,9 +202,11 @@ int add_gemm_problem(const char* op, bdattn::GemmLaunch& L, int idx, const void*
     const long long w_rows = geglu_offset > 0 ? static_cast<long long>(N) + geglu_offset : N;
     if (make_map_2d(op, &L.tmB[idx], W, L.bf16, K, w_rows, ldw, p.n_tile)) return -1;
     // 128 x 256 tiles need whole tiles along N and, for head tiles, unpadded heads of 64 or 128
-    L.wide[idx] = geglu_offset == 0 && N % 256 == 0 &&
-                  (head_dim == 0 || (head_dim == head_pad && (head_dim == 64 || head_dim == 128)));
-    if (L.wide[idx] && make_map_2d(op, &L.tmBw[idx], W, L.bf16, K, w_rows, ldw, 256)) return -1;
+    // (GEGLU: a tile is 128 value columns + their 128 gate columns, two 128-row boxes)
+    L.wide[idx] = geglu_offset > 0
+                      ? N % 128 == 0
+                      : N % 256 == 0 && (head_dim == 0 || (head_dim == head_pad && (head_dim == 64 || head_dim == 128)));
+    if (L.wide[idx] && make_map_2d(op, &L.tmBw[idx], W, L.bf16, K, w_rows, ldw, geglu_offset > 0 ? 128 : 256)) return -1;
     return 0;
 }
 

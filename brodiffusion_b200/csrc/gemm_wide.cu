@@ -12,8 +12,13 @@
 //   * the accumulator is double-buffered in tensor memory (2 x 256 columns),
 //     so the epilogue of tile i (bias, RMSNorm, RoPE, stores) runs while the
 //     MMAs of tile i+1 are issued.
+// GEGLU (src/fused_transformer.cu:89-92,275-282) runs here too: a tile is then
+// 128 value columns + their 128 gate columns (weight rows n0.. and D_out + n0..
+// loaded as the two halves of the B stage), one N = 256 MMA computes both and
+// the epilogue stores value * gelu_exact(gate).
 // Roles: warp 0 = TMA producer, warp 1 = tcgen05.mma issuer and TMEM owner,
-// warps 2-5 = epilogue (warp w owns TMEM lanes 32 * (w % 4)..).
+// warps 2-9 = epilogue (warp w owns TMEM lanes 32 * (w % 4)..; warps 2-5 take
+// the first half of a tile's output columns, warps 6-9 the second half).
 #include <cstdlib>
 
 #include "sdpa_internal.h"
@@ -22,7 +27,7 @@
 namespace bdattn {
 namespace {
 
-constexpr int kWThreads = 192;
+constexpr int kWThreads = 320;
 constexpr int kWStages = 4;
 constexpr int kWTileN = 256;
 constexpr int kWABytes = 128 * 64 * 2;        // A stage: 128 rows x 64 columns
@@ -34,21 +39,28 @@ struct WideTile {
     int z, m0, n0;
 };
 
+// Output columns of one tile: 256, or 128 for GEGLU (the other 128 accumulator
+// columns hold the gate).
+__host__ __device__ __forceinline__ int wide_out_cols(const GemmProblem& p) {
+    return p.geglu_offset > 0 ? kWTileN / 2 : kWTileN;
+}
+
 __device__ __forceinline__ WideTile wide_tile(const GemmArgs& g, int tile) {
     int z = 0;
     int local = tile;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int cnt = g.p[i].tiles_m * (g.p[i].N / kWTileN);
+        const int cnt = g.p[i].tiles_m * (g.p[i].N / wide_out_cols(g.p[i]));
         if (z == i && local >= cnt) {
             local -= cnt;
             z = i + 1;
         }
     }
     const int tm = z == 0 ? g.p[0].tiles_m : (z == 1 ? g.p[1].tiles_m : g.p[2].tiles_m);
+    const int wn = z == 0 ? wide_out_cols(g.p[0]) : (z == 1 ? wide_out_cols(g.p[1]) : wide_out_cols(g.p[2]));
     WideTile t;
     t.z = z;
-    t.n0 = (local / tm) * kWTileN;
+    t.n0 = (local / tm) * wn;
     t.m0 = (local % tm) * 128;
     return t;
 }
@@ -69,8 +81,12 @@ __device__ __forceinline__ float load16(const void* base, long long i) {
 // memory as FP32, or null for no RMSNorm.
 template <int HD, bool kBf16>
 __device__ __forceinline__ void epilogue_heads(const GemmProblem& p, uint32_t tacc, uint16_t* crow, int row,
-                                               int n0, const float* gain_s) {
-    constexpr int kHeads = kWTileN / HD;
+                                               int n0, const float* gain_s, int half) {
+    // this warp group's share of the tile: half of its heads
+    constexpr int kHeads = kWTileN / HD / 2;
+    tacc += static_cast<uint32_t>(half * (kWTileN / 2));
+    crow += half * (kWTileN / 2);
+    n0 += half * (kWTileN / 2);
     float inv[kHeads];
 #pragma unroll
     for (int h = 0; h < kHeads; ++h) inv[h] = 1.0f;
@@ -177,7 +193,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 128);
+            mbar_init(&acc_empty[s], 256);
         }
         fence_mbar_init();
     }
@@ -213,6 +229,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                 const CUtensorMap* tmA = t.z == 0 ? &tmA0 : (t.z == 1 ? &tmA1 : &tmA2);
                 const CUtensorMap* tmB = t.z == 0 ? &tmB0 : (t.z == 1 ? &tmB1 : &tmB2);
                 const int K = t.z == 0 ? g.p[0].K : (t.z == 1 ? g.p[1].K : g.p[2].K);
+                const int geglu_off = t.z == 0 ? g.p[0].geglu_offset : (t.z == 1 ? g.p[1].geglu_offset : g.p[2].geglu_offset);
                 const int k_blocks = (K + 63) / 64;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kWStages;
@@ -223,7 +240,13 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
                     uint8_t* st = smem + s * kWStageBytes;
                     mbar_arrive_expect_tx(&full[s], kWStageBytes);
                     tma_load_2d(st, tmA, &full[s], kb * 64, t.m0);
-                    tma_load_2d(st + kWABytes, tmB, &full[s], kb * 64, t.n0);
+                    if (geglu_off > 0) {
+                        // value rows, then the gate rows of the same output columns (128-row boxes)
+                        tma_load_2d(st + kWABytes, tmB, &full[s], kb * 64, t.n0);
+                        tma_load_2d(st + kWABytes + kWBBytes / 2, tmB, &full[s], kb * 64, geglu_off + t.n0);
+                    } else {
+                        tma_load_2d(st + kWABytes, tmB, &full[s], kb * 64, t.n0);
+                    }
                 }
             }
             if (!ok) {
@@ -272,7 +295,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
         }
     } else {
         // -------------------------------------------------------- epilogue
-        const int q = warp & 3;
+        const int q = warp & 3;             // TMEM lane quarter of this warp
+        const int half = (warp - 2) >> 2;   // which half of the tile's output columns
         int ti = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++ti) {
@@ -287,10 +311,41 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
             uint16_t* crow = reinterpret_cast<uint16_t*>(p.C) + static_cast<long long>(row) * p.ldc + t.n0;
             if (p.norm_rope) {
                 const float* gs = p.gain != nullptr ? gain_s + t.z * 128 : nullptr;
-                if (p.n_tile == 128) epilogue_heads<128, kBf16>(p, tacc, crow, row, t.n0, gs);
-                else epilogue_heads<64, kBf16>(p, tacc, crow, row, t.n0, gs);
+                if (p.n_tile == 128) epilogue_heads<128, kBf16>(p, tacc, crow, row, t.n0, gs, half);
+                else epilogue_heads<64, kBf16>(p, tacc, crow, row, t.n0, gs, half);
+            } else if (p.geglu_offset > 0) {
+                // value in accumulator columns [0, 128), gate in [128, 256); this group
+                // stores 64 of the tile's 128 output columns
+                for (int c = half * 64; c < half * 64 + 64; c += 32) {
+                    uint32_t v[32], gt[32];
+                    tmem_ld32(tacc + c, v);
+                    tmem_ld32(tacc + 128 + c, gt);
+                    tmem_wait_ld();
+                    float f[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float x = __uint_as_float(v[i]);
+                        float gate = __uint_as_float(gt[i]);
+                        if (p.bias != nullptr) {
+                            x += load16<kBf16>(p.bias, t.n0 + c + i);
+                            gate += load16<kBf16>(p.bias, p.geglu_offset + t.n0 + c + i);
+                        }
+                        f[i] = x * (0.5f * gate * (1.0f + erff(gate * 0.7071067811865475f)));
+                    }
+                    if (row < p.M) {
+#pragma unroll
+                        for (int v8 = 0; v8 < 4; ++v8) {
+                            uint4 w;
+                            w.x = pack2<kBf16>(f[v8 * 8 + 0], f[v8 * 8 + 1]);
+                            w.y = pack2<kBf16>(f[v8 * 8 + 2], f[v8 * 8 + 3]);
+                            w.z = pack2<kBf16>(f[v8 * 8 + 4], f[v8 * 8 + 5]);
+                            w.w = pack2<kBf16>(f[v8 * 8 + 6], f[v8 * 8 + 7]);
+                            *reinterpret_cast<uint4*>(crow + c + v8 * 8) = w;
+                        }
+                    }
+                }
             } else {
-                for (int c = 0; c < kWTileN; c += 32) {
+                for (int c = half * (kWTileN / 2); c < (half + 1) * (kWTileN / 2); c += 32) {
                     uint32_t v[32];
                     tmem_ld32(tacc + c, v);
                     tmem_wait_ld();
@@ -332,7 +387,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
 
 int gemm_wide_tiles(const GemmLaunch& L) {
     int total = 0;
-    for (int i = 0; i < L.n_problems; ++i) total += L.args.p[i].tiles_m * (L.args.p[i].N / kWTileN);
+    for (int i = 0; i < L.n_problems; ++i) total += L.args.p[i].tiles_m * (L.args.p[i].N / wide_out_cols(L.args.p[i]));
     return total;
 }
 

@@ -98,10 +98,11 @@ def test_linear(bd, oracle):
         G.check(G.host(y), oracle.linear(x, w, b), what=f"linear {M}x{N}x{K}")
 
 
-@pytest.mark.parametrize("B,Din,Dout", [(40, 64, 48), (128, 128, 96), (4096, 320, 1280)])
+@pytest.mark.parametrize("B,Din,Dout", [(40, 64, 48), (128, 128, 96), (4096, 320, 1280), (2300, 200, 1152)])
 def test_fused_linear_geglu(bd, oracle, golden, B, Din, Dout):
     """Reference shapes (tests/test_fused_parity.cpp:268-269) plus the SD1.5
-    top-level FF1 (4096, 320) -> 1280."""
+    top-level FF1 (4096, 320) -> 1280 and a ragged case; the last two are large
+    enough for the persistent wide-tile kernel (value + gate tile per MMA)."""
     if (B, Din, Dout) == (40, 64, 48):
         x, w, b = golden["geglu_x"], golden["geglu_w"], golden["geglu_b"]
         ref = golden["geglu_y"]
