@@ -314,9 +314,9 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 }
                 l_sum *= alpha;
                 if (j > 0) {
-                    ok = mbar_wait(&pv_done[t], static_cast<uint32_t>((j - 1) & 1));
-                    if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
-                    tc_fence_after();
+                    // P.V of step j-1 has completed: the commit that made S of this step
+                    // visible was issued after it and covers every earlier MMA of the
+                    // issuing thread
 #pragma unroll
                     for (int c = 0; c < HD / 32; ++c) {
                         uint32_t o[32];
@@ -369,7 +369,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
 
         if (ok && n_kv > 0) {
-            ok = mbar_wait(&pv_done[t], static_cast<uint32_t>((n_kv - 1) & 1));
+            ok = mbar_wait(&pv_done[t], 0u);       // committed once, after the last P.V
             ok = __all_sync(0xffffffffu, ok);
             tc_fence_after();
         }
@@ -498,10 +498,11 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 tc_fence_after();
                 if (lane == 0) {
                     issue_pv(0, vslot, j > 0);
-                    umma_commit(&pv_done[0]);
                     if (more) {
                         issue_qk(0, kslot);
                         umma_commit(&s_full[0]);
+                    } else {
+                        umma_commit(&pv_done[0]);    // only the last step needs its own signal
                     }
                 }
                 __syncwarp();
@@ -510,7 +511,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 tc_fence_after();
                 if (lane == 0) {
                     issue_pv(1, vslot, j > 0);
-                    umma_commit(&pv_done[1]);
+                    if (!more) umma_commit(&pv_done[1]);
                     umma_commit(&kv_empty[vslot]);
                     if (more) {
                         issue_qk(1, kslot);
