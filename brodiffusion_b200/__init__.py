@@ -47,6 +47,8 @@ class SdpaParams(C.Structure):
         ("key_mask", C.c_void_p), ("key_scale", C.c_void_p), ("val_scale", C.c_void_p),
         ("softmax_scale", C.c_float),
         ("num_kv_heads", C.c_int),
+        ("q_gain", C.c_void_p * 2), ("q_gain_dtype", C.c_int), ("q_eps", C.c_float),
+        ("q_cos", C.c_void_p), ("q_sin", C.c_void_p), ("q_rope_row0", C.c_int),
     ]
 
 
@@ -216,8 +218,8 @@ def device_status(clear: bool = True) -> int:
 
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
-             val_scale=None, softmax_scale=0.0, num_kv_heads=0, stream=None, peer_out_ptrs=None,
-             _trace=None):
+             val_scale=None, softmax_scale=0.0, num_kv_heads=0, q_norm=None, stream=None,
+             peer_out_ptrs=None, _trace=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
     (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
@@ -258,6 +260,18 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
     p.val_scale = val_scale.data_ptr() if val_scale is not None else None
     p.softmax_scale = softmax_scale
     p.num_kv_heads = num_kv_heads
+    if q_norm is not None:
+        # dict(gain=tensor | [per-segment tensors] | None, cos=, sin=, rope_row0=0, eps=1e-6):
+        # RMSNorm + RoPE of the query rows inside the attention kernel
+        gains = q_norm.get("gain")
+        gains = list(gains) if isinstance(gains, (list, tuple)) else [gains] * len(qs)
+        for i, gt in enumerate(gains[:2]):
+            p.q_gain[i] = _ptr(gt)
+        g0 = next((gt for gt in gains if gt is not None), None)
+        p.q_gain_dtype = _dtype_code(g0) if g0 is not None else F32
+        p.q_eps = q_norm.get("eps", 1e-6)
+        p.q_cos, p.q_sin = _ptr(q_norm.get("cos")), _ptr(q_norm.get("sin"))
+        p.q_rope_row0 = q_norm.get("rope_row0", 0)
     if _trace is not None:
         _check(lib().bdattn_sdpa_traced_fwd(C.byref(p), C.byref(_trace), _stream(stream)))
         return

@@ -295,6 +295,18 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
     const float scale = p->softmax_scale > 0.0f ? p->softmax_scale : 1.0f / std::sqrt(static_cast<float>(hd));
     const bool bf16 = p->dtype == BDATTN_BF16;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    const bool q_fused = p->q_gain[0] != nullptr || p->q_gain[1] != nullptr || p->q_cos != nullptr ||
+                         p->q_sin != nullptr;
+    if (q_fused) {
+        if ((p->q_cos == nullptr) != (p->q_sin == nullptr)) return fail("%s: q_cos and q_sin must both be given", op);
+        if (!aligned16(p->q_cos) || !aligned16(p->q_sin)) return fail("%s: q_cos and q_sin must be 16-byte aligned", op);
+        if ((p->q_gain[0] != nullptr || p->q_gain[1] != nullptr) && p->q_gain_dtype != BDATTN_F32 &&
+            p->q_gain_dtype != p->dtype)
+            return fail("%s: q_gain_dtype must be F32 or the tensor dtype", op);
+        if (!aligned16(p->q_gain[0]) || !aligned16(p->q_gain[1])) return fail("%s: q_gain must be 16-byte aligned", op);
+        if (p->q_rope_row0 < 0) return fail("%s: q_rope_row0 must be >= 0", op);
+        if (hd > 128) return fail("%s: the fused query RMSNorm/RoPE needs head_dim <= 128", op);
+    }
 
     if (hd <= 128) {
         // tensor-core path: the kernel computes with 64 or 128 columns per head and
@@ -333,6 +345,12 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         a.q_offset = static_cast<int>(Lk - Lq);
         a.hd_out = hd;
         a.kv_group = p->num_heads / nkv;
+        a.q_fused = q_fused ? 1 : 0;
+        a.q_gain[0] = p->q_gain[0];
+        a.q_gain[1] = p->n_q_seg > 1 ? p->q_gain[1] : p->q_gain[0];
+        a.q_gain_is_f32 = p->q_gain_dtype == BDATTN_F32 ? 1 : 0;
+        a.q_eps = p->q_eps;
+        a.q_cos = p->q_cos; a.q_sin = p->q_sin; a.q_rope_row0 = p->q_rope_row0;
         a.key_mask = p->key_mask;
         a.key_scale = p->key_scale;
         a.val_scale = p->val_scale;

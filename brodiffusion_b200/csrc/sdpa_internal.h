@@ -20,6 +20,14 @@ struct SdpaDevArgs {
     int q_offset;   // Lk - Lq
     int hd_out;     // columns stored per head
     int kv_group;   // query heads per K/V head (grouped-query attention), >= 1
+    // Query-side RMSNorm + RoPE done by the kernel on its Q tiles (all null: off).
+    int q_fused;
+    const void* q_gain[2];   // per query segment, hd_out values, or null
+    int q_gain_is_f32;
+    float q_eps;
+    const float* q_cos;      // (rows, hd_out / 2) FP32, or null
+    const float* q_sin;
+    int q_rope_row0;
     const float* key_mask;
     const float* key_scale;
     const float* val_scale;

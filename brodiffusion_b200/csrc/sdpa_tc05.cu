@@ -177,7 +177,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     uint64_t* s_full = kv_empty + ST;    // [2]
     uint64_t* p_full = s_full + 2;       // [2]
     uint64_t* pv_done = p_full + 2;      // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+    uint64_t* q_ready = pv_done + 2;     // [2]  Q tile normalised + rotated in place (fused Q path)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 2);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -211,6 +212,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             mbar_init(&s_full[t], 1);
             mbar_init(&p_full[t], 4);          // one arrival per softmax warp of the tile
             mbar_init(&pv_done[t], 1);
+            mbar_init(&q_ready[t], 4);
         }
         fence_mbar_init();
     }
@@ -242,6 +244,127 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         float m_ref = -INFINITY;
         float l_sum = 0.0f;
         bool ok = true;
+
+        if (a.q_fused && n_kv > 0) {
+            // Per-head RMSNorm + RoPE of the query tile, in place in the (128-byte
+            // swizzled) Q tile, before the first Q.K^T MMA (src/dit/flux.cpp:462-469 +
+            // src/dit/common.cpp:192 applied to Q).  A warp takes its 32 rows one at a
+            // time with the head's columns spread over the lanes, so that the cos / sin
+            // rows are read coalesced (one row per load; a thread-per-row version
+            // touched 32 cache lines per load and cost ten times as much).  Rows past
+            // the segment are zero and stay zero.
+            ok = __all_sync(0xffffffffu, mbar_wait(&q_full[t], 0));
+            if (ok) {
+                constexpr int kEpl = HD / 32;                 // elements per lane: 4 or 2
+                const int hd = a.hd_out;
+                const int c0 = lane * kEpl;                   // first column of this lane
+                const bool live = c0 < hd;                    // hd is a multiple of 8
+                const void* gain = qseg ? a.q_gain[1] : a.q_gain[0];
+                float gv[kEpl];
+#pragma unroll
+                for (int i = 0; i < kEpl; ++i) gv[i] = 1.0f;
+                if (gain != nullptr && live) {
+#pragma unroll
+                    for (int i = 0; i < kEpl; ++i) {
+                        if (a.q_gain_is_f32) gv[i] = __ldg(reinterpret_cast<const float*>(gain) + c0 + i);
+                        else {
+                            const uint16_t b = __ldg(reinterpret_cast<const uint16_t*>(gain) + c0 + i);
+                            gv[i] = kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                          : __half2float(*reinterpret_cast<const __half*>(&b));
+                        }
+                    }
+                }
+                const int bofs = (c0 & 63) * 2;               // byte offset inside the 128-byte row piece
+                uint8_t* qbase = smem_q + t * C::kQBytes + (c0 >> 6) * kChunkBytes + (bofs & 15);
+                const int cidx = bofs >> 4;
+                const float inv_hd = 1.0f / static_cast<float>(hd);
+                // 16 rows at a time, every load of a batch issued before the first use:
+                // a row-by-row loop is a chain of load and shuffle latencies
+                constexpr int kRb = 16;
+                const bool rope = a.q_cos != nullptr && live;
+#pragma unroll 1
+                for (int r0 = 0; r0 < 32; r0 += kRb) {
+                    uint32_t w[kRb][kEpl / 2];
+                    float cs[kRb][kEpl / 2], sn[kRb][kEpl / 2];
+#pragma unroll
+                    for (int k = 0; k < kRb; ++k) {
+                        const int r = (warp & 3) * 32 + r0 + k;
+                        const uint8_t* ptr = qbase + r * 128 + ((cidx ^ (r & 7)) << 4);
+                        if constexpr (kEpl == 4) {
+                            const uint2 u = *reinterpret_cast<const uint2*>(ptr);
+                            w[k][0] = u.x; w[k][1] = u.y;
+                        } else {
+                            w[k][0] = *reinterpret_cast<const uint32_t*>(ptr);
+                        }
+#pragma unroll
+                        for (int i = 0; i < kEpl / 2; ++i) { cs[k][i] = 1.0f; sn[k][i] = 0.0f; }
+                        if (rope && qrow0 + t * kBM + r < seg_rows) {
+                            const long long tb = static_cast<long long>(a.q_rope_row0 + q_global0 + t * kBM + r) * (hd >> 1) + (c0 >> 1);
+                            if constexpr (kEpl == 4) {
+                                const float2 cv = __ldg(reinterpret_cast<const float2*>(a.q_cos + tb));
+                                const float2 sv = __ldg(reinterpret_cast<const float2*>(a.q_sin + tb));
+                                cs[k][0] = cv.x; cs[k][1] = cv.y; sn[k][0] = sv.x; sn[k][1] = sv.y;
+                            } else {
+                                cs[k][0] = __ldg(a.q_cos + tb); sn[k][0] = __ldg(a.q_sin + tb);
+                            }
+                        }
+                    }
+                    float x[kRb][kEpl], ss[kRb];
+#pragma unroll
+                    for (int k = 0; k < kRb; ++k) {
+#pragma unroll
+                        for (int i = 0; i < kEpl / 2; ++i) {
+                            if constexpr (kBf16) {
+                                x[k][2 * i] = __uint_as_float(w[k][i] << 16);
+                                x[k][2 * i + 1] = __uint_as_float(w[k][i] & 0xffff0000u);
+                            } else {
+                                const __half2 h = *reinterpret_cast<const __half2*>(&w[k][i]);
+                                x[k][2 * i] = __low2float(h);
+                                x[k][2 * i + 1] = __high2float(h);
+                            }
+                        }
+                        ss[k] = 0.0f;
+#pragma unroll
+                        for (int i = 0; i < kEpl; ++i) ss[k] = fmaf(x[k][i], x[k][i], ss[k]);
+                    }
+                    if (gain != nullptr) {
+#pragma unroll
+                        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+                            for (int k = 0; k < kRb; ++k) ss[k] += __shfl_xor_sync(0xffffffffu, ss[k], o);
+                        }
+#pragma unroll
+                        for (int k = 0; k < kRb; ++k) {
+                            const float inv = rsqrtf(ss[k] * inv_hd + a.q_eps);
+#pragma unroll
+                            for (int i = 0; i < kEpl; ++i) x[k][i] *= inv * gv[i];
+                        }
+                    }
+#pragma unroll
+                    for (int k = 0; k < kRb; ++k) {
+                        const int r = (warp & 3) * 32 + r0 + k;
+                        uint8_t* ptr = qbase + r * 128 + ((cidx ^ (r & 7)) << 4);
+#pragma unroll
+                        for (int i = 0; i < kEpl / 2; ++i) {
+                            const float a0 = x[k][2 * i], b0 = x[k][2 * i + 1];
+                            x[k][2 * i] = a0 * cs[k][i] - b0 * sn[k][i];
+                            x[k][2 * i + 1] = a0 * sn[k][i] + b0 * cs[k][i];
+                        }
+                        if constexpr (kEpl == 4) {
+                            uint2 u;
+                            u.x = pack2<kBf16>(x[k][0], x[k][1]);
+                            u.y = pack2<kBf16>(x[k][2], x[k][3]);
+                            *reinterpret_cast<uint2*>(ptr) = u;
+                        } else {
+                            *reinterpret_cast<uint32_t*>(ptr) = pack2<kBf16>(x[k][0], x[k][1]);
+                        }
+                    }
+                }
+                fence_proxy_async_smem();      // the MMA reads the tile through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&q_ready[t]);
+            }
+        }
 
         for (int j = 0; j < n_kv; ++j) {
             ok = mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1));
@@ -472,6 +595,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 
             bool ok = n_kv > 0;
             if (ok) ok = mbar_wait(&q_full[0], 0) && mbar_wait(&q_full[1], 0);
+            if (ok && a.q_fused) ok = mbar_wait(&q_ready[0], 0) && mbar_wait(&q_ready[1], 0);
             if (ok) ok = mbar_wait(&kv_full[0], 0);
             if (ok) {
                 tc_fence_after();

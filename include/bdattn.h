@@ -123,6 +123,25 @@ typedef struct bdattn_sdpa_params {
      * Krep / Vrep copies of the reference (common.cpp:361-375) are never made.
      * 0 or num_heads = plain multi-head attention; must divide num_heads. */
     int num_kv_heads;
+    /* Optional per-head RMSNorm + RoPE of the QUERY rows inside the kernel (the
+     * headnorm + rope_apply of Q in src/dit/flux.cpp:462-469,
+     * src/dit/common.cpp:192 and src/dit/qwenimage21_forward.cpp:54-63,584):
+     * every CTA normalises and rotates its own query tile in shared memory
+     * before the first MMA, so the Q half of the bdattn_rmsnorm_rope pre-pass
+     * and its HBM round trip disappear.  (K is not fused: every query-tile CTA
+     * of a head would repeat that work.)
+     *   q_gain[s]   head_dim gains of query segment s (q_gain_dtype: F32 or the
+     *               tensor dtype), or NULL for no RMSNorm on that segment
+     *   q_cos/q_sin FP32 (rows, head_dim/2) tables, interleaved pairs, or NULL;
+     *               query row i of the concatenated segments uses table row
+     *               q_rope_row0 + i
+     * All NULL = disabled.  head_dim <= 128 only. */
+    const void* q_gain[2];
+    int q_gain_dtype;
+    float q_eps;
+    const float* q_cos;
+    const float* q_sin;
+    int q_rope_row0;
 } bdattn_sdpa_params;
 
 int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);

@@ -282,6 +282,50 @@ def test_grouped_query_heads_refusals(bd):
         bd.sdpa_fwd(q, kv2, kv2, torch.empty_like(q), 8, num_kv_heads=4)
 
 
+@pytest.mark.parametrize("nh,hd,axes", [(2, 128, (16, 56, 56)), (3, 64, (8, 28, 28)), (2, 40, (8, 16, 16))])
+def test_query_norm_and_rope_inside_the_kernel(bd, oracle, nh, hd, axes):
+    """The Q half of the RMSNorm + RoPE pre-pass done by the attention kernel on
+    its own query tiles (headnorm + rope_apply of Q, src/dit/flux.cpp:462-469,
+    src/dit/common.cpp:192): text and image query segments with their own gains
+    (norm_added_q / norm_q), table rows offset per segment, ragged image length;
+    K is normalised and rotated beforehand as in the pre-pass.  Checked against
+    the oracle and against the pre-pass path."""
+    txt, hp, wp = 77, 18, 17
+    img = hp * wp
+    D = nh * hd
+    q = synth.activations((txt + img, D), 9900 + hd)
+    k = synth.activations((txt + img, D), 9901 + hd)
+    v = synth.activations((txt + img, D), 9902 + hd)
+    g_txt, g_img = synth.gains(hd, 9903, "f32"), synth.gains(hd, 9904, "f32")
+    cos, sin = oracle.flux_rope_tables(txt, hp, wp, hd, axes)
+    # oracle: norm + rope of Q per segment, K likewise (one gain is enough for K here)
+    def nr(x, g, r0):
+        return oracle.rope_apply(oracle.rms_norm_heads(x, nh, hd, g), nh, hd, cos[r0:], sin[r0:])
+    qr = np.concatenate([nr(q[:txt], g_txt, 0), nr(q[txt:], g_img, txt)])
+    kr = synth.round_bf16(np.concatenate([nr(k[:txt], g_txt, 0), nr(k[txt:], g_img, txt)]))
+    ref = oracle.sdpa(synth.round_bf16(qr), kr, v, nh)
+    tq, tk, tv = G.dev(q), G.dev(kr), G.dev(v)
+    tcos, tsin = G.dev(cos, torch.float32), G.dev(sin, torch.float32)
+    out = torch.full_like(tq, float("nan"))
+    bd.sdpa_fwd([tq[:txt], tq[txt:]], tk, tv, [out[:txt], out[txt:]], nh,
+                q_norm=dict(gain=[G.dev(g_txt, torch.float32), G.dev(g_img, torch.float32)], cos=tcos, sin=tsin))
+    assert bd.device_status() == 0
+    G.check(G.host(out), ref, what=f"fused query norm+rope hd={hd}")
+    # the pre-pass path on the same inputs
+    tqr = torch.empty_like(tq)
+    bd.rmsnorm_rope([dict(x=tq[:txt], out=tqr[:txt], gain=G.dev(g_txt, torch.float32), cos=tcos, sin=tsin, rope_row0=0),
+                     dict(x=tq[txt:], out=tqr[txt:], gain=G.dev(g_img, torch.float32), cos=tcos, sin=tsin, rope_row0=txt)],
+                    nh, hd)
+    out2 = torch.full_like(tq, float("nan"))
+    bd.sdpa_fwd(tqr, tk, tv, out2, nh)
+    assert (out.float() - out2.float()).abs().max().item() < 4e-3
+    # RoPE only (no gains), one segment, rows offset into the table
+    out3 = torch.full_like(tq[txt:], float("nan"))
+    bd.sdpa_fwd(tq[txt:], tk, tv, out3, nh, q_norm=dict(gain=None, cos=tcos, sin=tsin, rope_row0=txt))
+    ref3 = oracle.sdpa(synth.round_bf16(oracle.rope_apply(q[txt:], nh, hd, cos[txt:], sin[txt:])), kr, v, nh)
+    G.check(G.host(out3), ref3, what=f"fused query rope only hd={hd}")
+
+
 # --------------------------------------------------------------- edge cases
 @pytest.mark.parametrize("hd", [128, 64, 40, 72, 112, 160])
 @pytest.mark.parametrize("L", [1, 63, 64, 65, 127, 129, 257])
