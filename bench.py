@@ -6,10 +6,11 @@
 
 One step = one pass of the hot path over one synthetic batch:
   flux1024              (1 GPU)  Flux.1 joint attention at 1024 px, double-stream
-                        form: per-head RMSNorm + 3-axis RoPE of K (one launch, two
-                        jobs), then the joint softmax attention of 512 text + 4096
-                        image tokens, 24 heads x 128 (one launch), which applies
-                        RMSNorm + RoPE to its own query tiles.
+                        form: per-head QK RMSNorm + 3-axis RoPE (one launch, four
+                        jobs) and the joint softmax attention of 512 text + 4096
+                        image tokens, 24 heads x 128 (one launch).  With --q-norm
+                        fused the attention kernel normalises and rotates its own
+                        query tiles and the pre-pass handles K only.
   flux2048_headsharded  (N GPUs) Flux.1 joint attention at 2048 px, batch 2,
                         512 + 16384 tokens; heads split over the ranks, NCCL
                         all-gather of the per-head outputs.  Default for N > 1.
