@@ -69,10 +69,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// ReLU of two packed BF16 values: the fused multiply-add with the ReLU modifier
+// (x * 1 + 0) runs on the FMA pipe; the packed maximum against zero issues at a
+// quarter of that rate on this part.
 __device__ __forceinline__ uint32_t relu2(uint32_t w) {
-    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&w);
-    x = __hmax2(x, __float2bfloat162_rn(0.0f));
-    return *reinterpret_cast<uint32_t*>(&x);
+    uint32_t r;
+    asm("fma.rn.relu.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(w), "r"(0x3f803f80u), "r"(0u));
+    return r;
 }
 __device__ __forceinline__ float sum2(uint32_t w) {
     return __uint_as_float(w << 16) + __uint_as_float(w & 0xffff0000u);
