@@ -38,11 +38,14 @@ constexpr int kLaMaxStages = 8;               // ring of 16 KB items: 8 with one
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
 constexpr int kLaState = 33 * 32;             // [S; z] floats
+constexpr int kLaStLd = 40;                   // row stride of the state tile in shared memory: the fragment
+                                              // loads of the apply pass (rows over g, columns over q4) then
+                                              // meet at most two to a bank instead of eight
 
 struct LaSmem {
     float partial[kLaWarps][kLaState];
     float local_state[kLaState];
-    float state[48 * 32];   // rows 33..47 zero
+    float state[48 * kLaStLd];   // rows 33..47 zero
     alignas(1024) uint8_t out_stage[2][2 * kLaBoxBytes];   // two 32 x 128-token output tiles, box layout
     uint64_t full[kLaMaxStages];
     uint64_t empty[kLaMaxStages];
@@ -128,7 +131,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         }
         fence_mbar_init();
     }
-    for (int i = tid; i < 48 * 32; i += kLaThreads) sm.state[i] = 0.0f;
+    for (int i = tid; i < 48 * kLaStLd; i += kLaThreads) sm.state[i] = 0.0f;
     __syncthreads();
 
     if (warp == kLaWarps) {
@@ -229,18 +232,15 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
 
     // reduce: warps -> CTA (shared memory) -> cluster (distributed shared memory)
+    // accumulators are parked in fragment order (register slot x lane: every store
+    // is 32 consecutive floats, no bank conflicts); the sum over the warps below
+    // puts each element at its place in the matrix
 #pragma unroll
     for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int nt = 0; nt < 4; ++nt) {
-            float* p = sm.partial[warp];
-            const int i0 = mt * 16 + g;
-            const int j0 = nt * 8 + q4 * 2;
-            p[i0 * 32 + j0] = acc[mt][nt][0];
-            p[i0 * 32 + j0 + 1] = acc[mt][nt][1];
-            p[(i0 + 8) * 32 + j0] = acc[mt][nt][2];
-            p[(i0 + 8) * 32 + j0 + 1] = acc[mt][nt][3];
-        }
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) sm.partial[warp][((mt * 4 + nt) * 4 + r) * 32 + lane] = acc[mt][nt][r];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
         float z = zacc[nt];
@@ -253,7 +253,14 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float s = 0.0f;
 #pragma unroll
         for (int w = 0; w < kLaWarps; ++w) s += sm.partial[w][i];
-        sm.local_state[i] = s;
+        int at = i;                                   // the z row is stored in place
+        if (i < 32 * 32) {
+            const int slot = i >> 5, ln = i & 31;     // slot = (mt * 4 + nt) * 4 + r
+            const int row = (slot >> 4) * 16 + (ln >> 2) + ((slot >> 1) & 1) * 8;
+            const int col = ((slot >> 2) & 3) * 8 + (ln & 3) * 2 + (slot & 1);
+            at = row * 32 + col;
+        }
+        sm.local_state[at] = s;
     }
     phase_sync();
     {
@@ -284,7 +291,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 const long long so = (static_cast<long long>(batch) * a.num_heads + head) * kLaState + i;
                 if (a.sz_out != nullptr && rank == 0) a.sz_out[so] = s;
                 if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
-                sm.state[i] = s;
+                sm.state[(i >> 5) * kLaStLd + (i & 31)] = s;
             }
         }
     }
@@ -305,8 +312,8 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int r = 0; r < 4; ++r) {
                 const int row = mt * 16 + g + (r & 1) * 8;
                 const int col = ks * 16 + q4 * 2 + (r >> 1) * 8;
-                const float x0 = sm.state[row * 32 + col];
-                const float x1 = sm.state[row * 32 + col + 1];
+                const float2 xx = *reinterpret_cast<const float2*>(&sm.state[row * kLaStLd + col]);
+                const float x0 = xx.x, x1 = xx.y;
                 ah[mt][ks][r] = pack2<true>(x0, x1);
             }
 
