@@ -260,10 +260,18 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const int col = ((slot >> 2) & 3) * 8 + (ln & 3) * 2 + (slot & 1);
             at = row * 32 + col;
         }
-        sm.local_state[at] = s;
+        if (cs == 1) {
+            // no partner CTA: this is the final state (capture / inject seam applied here)
+            const long long so = (static_cast<long long>(batch) * a.num_heads + head) * kLaState + at;
+            if (a.sz_out != nullptr) a.sz_out[so] = s;
+            if (a.sz_in != nullptr) s += a.w_in * a.sz_in[so];
+            sm.state[(at >> 5) * kLaStLd + (at & 31)] = s;
+        } else {
+            sm.local_state[at] = s;
+        }
     }
     phase_sync();
-    {
+    if (cs > 1) {
         // every thread owns up to five state elements; all remote (distributed
         // shared memory) loads are issued before the first add so that their
         // latencies overlap
@@ -276,7 +284,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             for (int r = 0; r < 8; ++r) {
                 part[e][r] = 0.0f;
                 if (r < cs && i < kLaState) {
-                    const float* remote = cs == 1 ? sm.local_state : cluster.map_shared_rank(sm.local_state, r);
+                    const float* remote = cluster.map_shared_rank(sm.local_state, r);
                     part[e][r] = remote[i];
                 }
             }
