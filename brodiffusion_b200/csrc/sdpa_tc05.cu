@@ -378,11 +378,26 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             tmem_wait_ld();
 
             const TileInfo ti = kv_tile(a, j);
+            // Per-key vectors of the hooks are read by 16-byte loads on full,
+            // aligned tiles (the same addresses for every thread: broadcast loads);
+            // ragged or unaligned tiles take the element-wise path.
+            auto hook_vec = [&](const float* p) {
+                return ti.valid == kBN && ((reinterpret_cast<uintptr_t>(p + ti.kbase) & 15u) == 0);
+            };
             if constexpr (kHooks) {
                 if (a.key_scale != nullptr) {
+                    if (hook_vec(a.key_scale)) {
+                        const float4* kv4 = reinterpret_cast<const float4*>(a.key_scale + ti.kbase);
 #pragma unroll
-                    for (int c = 0; c < kBN; ++c) {
-                        if (c < ti.valid) s[c] *= __ldg(a.key_scale + ti.kbase + c);
+                        for (int c4 = 0; c4 < kBN / 4; ++c4) {
+                            const float4 f = __ldg(kv4 + c4);
+                            s[4 * c4] *= f.x; s[4 * c4 + 1] *= f.y; s[4 * c4 + 2] *= f.z; s[4 * c4 + 3] *= f.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kBN; ++c) {
+                            if (c < ti.valid) s[c] *= __ldg(a.key_scale + ti.kbase + c);
+                        }
                     }
                 }
             }
@@ -406,9 +421,21 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             }
             if constexpr (kHooks) {
                 if (a.key_mask != nullptr) {
+                    if (hook_vec(a.key_mask)) {
+                        const float4* km4 = reinterpret_cast<const float4*>(a.key_mask + ti.kbase);
 #pragma unroll
-                    for (int c = 0; c < kBN; ++c) {
-                        if (c < ti.valid && __ldg(a.key_mask + ti.kbase + c) == 0.0f) s[c] = -INFINITY;
+                        for (int c4 = 0; c4 < kBN / 4; ++c4) {
+                            const float4 f = __ldg(km4 + c4);
+                            if (f.x == 0.0f) s[4 * c4] = -INFINITY;
+                            if (f.y == 0.0f) s[4 * c4 + 1] = -INFINITY;
+                            if (f.z == 0.0f) s[4 * c4 + 2] = -INFINITY;
+                            if (f.w == 0.0f) s[4 * c4 + 3] = -INFINITY;
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kBN; ++c) {
+                            if (c < ti.valid && __ldg(a.key_mask + ti.kbase + c) == 0.0f) s[c] = -INFINITY;
+                        }
                     }
                 }
             }
@@ -460,6 +487,23 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 uint32_t pk[16];
+                float vsc[32];
+                if constexpr (kHooks) {
+                    if (a.val_scale != nullptr) {
+                        if (hook_vec(a.val_scale)) {
+                            const float4* vs4 = reinterpret_cast<const float4*>(a.val_scale + ti.kbase + ch * 32);
+#pragma unroll
+                            for (int c4 = 0; c4 < 8; ++c4) {
+                                const float4 f = __ldg(vs4 + c4);
+                                vsc[4 * c4] = f.x; vsc[4 * c4 + 1] = f.y; vsc[4 * c4 + 2] = f.z; vsc[4 * c4 + 3] = f.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 32; ++c)
+                                vsc[c] = (ch * 32 + c < ti.valid) ? __ldg(a.val_scale + ti.kbase + ch * 32 + c) : 1.0f;
+                        }
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int c0 = ch * 32 + 2 * i;
@@ -474,8 +518,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
                     if constexpr (kHooks) {
                         if (a.val_scale != nullptr) {
-                            if (c0 < ti.valid) p0 *= __ldg(a.val_scale + ti.kbase + c0);
-                            if (c0 + 1 < ti.valid) p1 *= __ldg(a.val_scale + ti.kbase + c0 + 1);
+                            p0 *= vsc[2 * i];
+                            p1 *= vsc[2 * i + 1];
                         }
                     }
                     pk[i] = pack2<kBf16>(p0, p1);
