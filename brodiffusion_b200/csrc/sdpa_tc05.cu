@@ -367,6 +367,22 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         }
 
         for (int j = 0; j < n_kv; ++j) {
+            // Key mask of this tile as 128 bits (four ballots over one coalesced load
+            // per lane), fetched before the wait for S so that its latency is hidden.
+            uint32_t mbits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+            if constexpr (kHooks) {
+                if (a.key_mask != nullptr) {
+                    const TileInfo tm = kv_tile(a, j);
+                    float mv[4];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const int c = 4 * lane + w;
+                        mv[w] = c < tm.valid ? __ldg(a.key_mask + tm.kbase + c) : 1.0f;
+                    }
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) mbits[w] = __ballot_sync(0xffffffffu, mv[w] != 0.0f);
+                }
+            }
             ok = mbar_wait(&s_full[t], static_cast<uint32_t>(j & 1));
             if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
             tc_fence_after();
@@ -420,22 +436,11 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 for (int c = 0; c < kBN; ++c) s[c] = (c <= lim) ? s[c] : -INFINITY;
             }
             if constexpr (kHooks) {
-                if (a.key_mask != nullptr) {
-                    if (hook_vec(a.key_mask)) {
-                        const float4* km4 = reinterpret_cast<const float4*>(a.key_mask + ti.kbase);
+                // (tiles without a masked key, the usual case away from the padded tail, skip this)
+                if (a.key_mask != nullptr && (mbits[0] & mbits[1] & mbits[2] & mbits[3]) != 0xffffffffu) {
 #pragma unroll
-                        for (int c4 = 0; c4 < kBN / 4; ++c4) {
-                            const float4 f = __ldg(km4 + c4);
-                            if (f.x == 0.0f) s[4 * c4] = -INFINITY;
-                            if (f.y == 0.0f) s[4 * c4 + 1] = -INFINITY;
-                            if (f.z == 0.0f) s[4 * c4 + 2] = -INFINITY;
-                            if (f.w == 0.0f) s[4 * c4 + 3] = -INFINITY;
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < kBN; ++c) {
-                            if (c < ti.valid && __ldg(a.key_mask + ti.kbase + c) == 0.0f) s[c] = -INFINITY;
-                        }
+                    for (int c = 0; c < kBN; ++c) {
+                        if (((mbits[c & 3] >> (c >> 2)) & 1u) == 0u) s[c] = -INFINITY;
                     }
                 }
             }
