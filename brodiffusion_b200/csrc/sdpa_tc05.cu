@@ -155,9 +155,10 @@ __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// HOOKS: key_mask / key_scale / val_scale are honoured (slower softmax path).
+// HOOKS: 0 = none; 1 = key_mask only; 2 = key_mask, key_scale, val_scale, bias and the
+// per-row softmax statistics (slower softmax path).
 // EMU  : of every 8 consecutive exponentials, EMU are evaluated by polynomial.
-template <int HD, bool kBf16, bool kHooks, int kEmu>
+template <int HD, bool kBf16, int kHooks, int kEmu>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                  const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
@@ -370,7 +371,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             // Key mask of this tile as 128 bits (four ballots over one coalesced load
             // per lane), fetched before the wait for S so that its latency is hidden.
             uint32_t mbits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-            if constexpr (kHooks) {
+            if constexpr (kHooks >= 1) {
                 if (a.key_mask != nullptr) {
                     const TileInfo tm = kv_tile(a, j);
                     float mv[4];
@@ -400,7 +401,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             auto hook_vec = [&](const float* p) {
                 return ti.valid == kBN && ((reinterpret_cast<uintptr_t>(p + ti.kbase) & 15u) == 0);
             };
-            if constexpr (kHooks) {
+            if constexpr (kHooks == 2) {
                 if (a.key_scale != nullptr) {
                     if (hook_vec(a.key_scale)) {
                         const float4* kv4 = reinterpret_cast<const float4*>(a.key_scale + ti.kbase);
@@ -417,7 +418,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     }
                 }
             }
-            if constexpr (kHooks) {
+            if constexpr (kHooks == 2) {
                 if (a.bias != nullptr) {
                     const int br = q_glob - a.bias_row0;
                     if (br >= 0 && br < a.bias_rows && ti.kbase < a.bias_cols) {
@@ -435,7 +436,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 #pragma unroll
                 for (int c = 0; c < kBN; ++c) s[c] = (c <= lim) ? s[c] : -INFINITY;
             }
-            if constexpr (kHooks) {
+            if constexpr (kHooks >= 1) {
                 // (tiles without a masked key, the usual case away from the padded tail, skip this)
                 if (a.key_mask != nullptr && (mbits[0] & mbits[1] & mbits[2] & mbits[3]) != 0xffffffffu) {
 #pragma unroll
@@ -493,7 +494,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             for (int ch = 0; ch < 4; ++ch) {
                 uint32_t pk[16];
                 float vsc[32];
-                if constexpr (kHooks) {
+                if constexpr (kHooks == 2) {
                     if (a.val_scale != nullptr) {
                         if (hook_vec(a.val_scale)) {
                             const float4* vs4 = reinterpret_cast<const float4*>(a.val_scale + ti.kbase + ch * 32);
@@ -521,7 +522,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                         p1 = fast_exp2(x1);
                     }
                     fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
-                    if constexpr (kHooks) {
+                    if constexpr (kHooks == 2) {
                         if (a.val_scale != nullptr) {
                             p0 *= vsc[2 * i];
                             p1 *= vsc[2 * i + 1];
@@ -546,7 +547,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             tc_fence_after();
         }
         const float inv = (l_sum > 0.0f) ? 1.0f / l_sum : 0.0f;
-        if constexpr (kHooks) {
+        if constexpr (kHooks == 2) {
             if (a.lse != nullptr && ok && row_in_seg < seg_rows) {
                 float* st = a.lse + ((static_cast<long long>(batch) * gridDim.y + head) * a.lq_total + q_glob) * 2;
                 st[0] = m_ref * sl2;
@@ -747,7 +748,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     }
 }
 
-template <int HD, bool kBf16, bool kHooks, int kEmu>
+template <int HD, bool kBf16, int kHooks, int kEmu>
 cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     using C = Cfg<HD>;
     auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks, kEmu>;
@@ -769,14 +770,17 @@ cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
 
 template <int HD, bool kBf16>
 cudaError_t launch_hd(const SdpaLaunch& L, cudaStream_t stream) {
-    const bool hooks = L.args.key_mask != nullptr || L.args.key_scale != nullptr ||
-                       L.args.val_scale != nullptr || L.args.bias != nullptr || L.args.lse != nullptr;
-    if (hooks) return launch_t<HD, kBf16, true, 0>(L, stream);
+    // 2: every hook; 1: key mask only (the common case: padded captions), kept free of
+    // the other hooks' code; 0: none
+    const bool all_hooks = L.args.key_scale != nullptr || L.args.val_scale != nullptr ||
+                           L.args.bias != nullptr || L.args.lse != nullptr;
+    if (all_hooks) return launch_t<HD, kBf16, 2, 0>(L, stream);
+    if (L.args.key_mask != nullptr) return launch_t<HD, kBf16, 1, 0>(L, stream);
     switch (L.emu) {
-        case 0: return launch_t<HD, kBf16, false, 0>(L, stream);
-        case 2: return launch_t<HD, kBf16, false, 2>(L, stream);
-        case 6: return launch_t<HD, kBf16, false, 6>(L, stream);
-        default: return launch_t<HD, kBf16, false, 4>(L, stream);
+        case 0: return launch_t<HD, kBf16, 0, 0>(L, stream);
+        case 2: return launch_t<HD, kBf16, 0, 2>(L, stream);
+        case 6: return launch_t<HD, kBf16, 0, 6>(L, stream);
+        default: return launch_t<HD, kBf16, 0, 4>(L, stream);
     }
 }
 
