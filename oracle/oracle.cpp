@@ -10,8 +10,15 @@
 //   * softmax attention core  : follows brodiffusion's own host loop
 //     dit::joint_attention_traced (src/dit/common.cpp:246-305) statement by
 //     statement (double scores, stable softmax, float P.V accumulation).
-//   * RoPE tables             : follow src/dit/common.cpp:116-184 (Flux) and
-//     src/dit/qwenimage21_forward.cpp:136-196 (Qwen-Image).
+//     PINNED: that source file is compiled unmodified (Makefile target
+//     _ref/libref.so, host-only brotensor stand-in in ref_stub/) and
+//     tests/test_oracle_pin.py holds bdo_sdpa to it: head-averaged maps
+//     bit-identical, outputs within one FP32 ulp; its outputs on seeded inputs
+//     are committed as tests/golden/ref_pin.npz.
+//   * Flux RoPE tables        : follow src/dit/common.cpp:116-184.  PINNED the
+//     same way, bit-identical.
+//   * Qwen-Image RoPE tables  : follow src/dit/qwenimage21_forward.cpp:136-196
+//     (a member function of the model class; not compilable on its own).
 //   * ReLU linear attention   : follows src/dit/sana.cpp:470-520.
 //   * SD1.5 attention block   : follows src/unet_blocks.cpp:253-330.
 //   * GEGLU                   : follows src/fused_transformer.cu:89-92,275-282.
