@@ -46,7 +46,7 @@ WORKLOADS = {
 # Sana 1600M ReLU linear attention (config 4): name -> (batch, heads, tokens); 1 GPU, HBM-bound.
 SANA_WORKLOADS = {"sana1024": (2, 70, 1024), "sana4096": (2, 70, 4096)}
 # dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_tc05_kernel launch
-# on the flux1024 workload, from the ncu capture summarised under profiles/.
+# on the flux1024 workload, from one ncu capture of that launch.
 NCU_TRAFFIC_BYTES = {"flux1024": 84.99e6 + 6.07e6}
 
 
@@ -490,7 +490,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 def run_sana(args):
-    """Config 4 on one GPU: one step = one bdattn_linear_attn_relu_fwd call on a
+    """Sana 1600M linear attention on one GPU: one step = one bdattn_linear_attn_relu_fwd call on a
     (batch, 2240, tokens) channel-major BF16 problem; metric = algorithmic GB/s
     (4 * tokens * 2240 * 2 bytes per batch item).  Steps are replayed from a
     CUDA graph so that host launch gaps do not enter the device time."""

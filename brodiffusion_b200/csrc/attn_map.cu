@@ -72,9 +72,14 @@ __global__ void __launch_bounds__(128) attn_map_kernel(const AttnMapArgs a) {
             float dot = 0.0f;
             for (int d = 0; d < hd; ++d) dot = fmaf(Qs[r * hdp + d], Ks[kk * hdp + d], dot);
             float x = dot * a.scale_log2;
+            bool visible = kg < a.map_cols;
+            if (visible && a.key_scale != nullptr) x *= __ldg(a.key_scale + kg);
             if (biased && kg < a.bias_cols) x += __ldg(a.bias + static_cast<long long>(br) * a.bias_ld + kg) * log2e;
+            // the same visibility rules as the attention kernel: a masked key has weight 0
+            if (a.mask_mode == 1 && kg > qi + a.q_offset) visible = false;
+            if (visible && a.key_mask != nullptr && __ldg(a.key_mask + kg) == 0.0f) visible = false;
             // a row whose reference maximum is -inf saw no key: its map row is zero
-            const float p = (m2 == -INFINITY) ? 0.0f : exp2f(x - m2) * inv_l;
+            const float p = (!visible || m2 == -INFINITY) ? 0.0f : exp2f(x - m2) * inv_l;
             acc[i] += p;
         }
     }
@@ -93,13 +98,17 @@ __global__ void __launch_bounds__(128) attn_map_kernel(const AttnMapArgs a) {
 cudaError_t launch_attn_map(const AttnMapArgs& a, bool bf16, cudaStream_t stream) {
     const size_t smem = sizeof(float) * 2 * 32 * (a.head_dim + 1);
     dim3 grid(static_cast<unsigned>((a.map_cols + 31) / 32), static_cast<unsigned>((a.map_rows + 31) / 32));
+    // 2 x 32 x 257 floats at head_dim 256 is the most this kernel asks for; the
+    // limit is raised to that once per device and kernel, not on every launch.
+    constexpr int kMaxSmem = static_cast<int>(sizeof(float) * 2 * 32 * (256 + 1));
+    if (static_cast<int>(smem) > kMaxSmem) return cudaErrorInvalidValue;
     cudaError_t e;
     if (bf16) {
-        e = cudaFuncSetAttribute(attn_map_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        e = set_max_smem_once(attn_map_kernel<true>, kMaxSmem);
         if (e != cudaSuccess) return e;
         attn_map_kernel<true><<<grid, 128, smem, stream>>>(a);
     } else {
-        e = cudaFuncSetAttribute(attn_map_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        e = set_max_smem_once(attn_map_kernel<false>, kMaxSmem);
         if (e != cudaSuccess) return e;
         attn_map_kernel<false><<<grid, 128, smem, stream>>>(a);
     }

@@ -92,17 +92,6 @@ int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
     return 0;
 }
 
-// Share of the softmax exponentials evaluated on the FMA pipe (of every 8).
-// BDATTN_SDPA_EMU overrides the default for tuning runs.
-int sdpa_emu_setting() {
-    static int v = [] {
-        const char* e = std::getenv("BDATTN_SDPA_EMU");
-        int x = e ? std::atoi(e) : 0;
-        return (x == 0 || x == 2 || x == 4 || x == 6) ? x : 0;
-    }();
-    return v;
-}
-
 // Attention operand: (head_dim, heads, rows, batch) view of a row-major
 // (rows, heads * head_dim) 16-bit tensor; box = 64 head elements x 1 head x
 // box_rows rows, 128-byte swizzle.  Head elements beyond head_dim read as zero.
@@ -174,6 +163,12 @@ int add_gemm_problem(const char* op, bdattn::GemmLaunch& L, int idx, const void*
         return fail("%s: inner size and row strides must be multiples of 8 elements (K=%d lda=%lld ldw=%lld "
                     "ldc=%lld)", op, K, lda, ldw, ldc);
     if (!aligned16(A) || !aligned16(W) || !aligned16(Cout)) return fail("%s: matrices must be 16-byte aligned", op);
+    {
+        // columns one output row receives: N, or head_pad per head for head tiles
+        const long long written = head_dim > 0 ? static_cast<long long>(N / head_dim) * head_pad : N;
+        if (ldc < written)
+            return fail("%s: output row stride %lld is smaller than the %lld columns written per row", op, ldc, written);
+    }
     bdattn::GemmProblem& p = L.args.p[idx];
     p.M = M; p.N = N; p.K = K; p.C = Cout; p.ldc = ldc; p.bias = bias;
     p.tiles_m = (M + 127) / 128;
@@ -379,7 +374,6 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         L.batch = p->batch;
         L.head_dim = hd_kernel;
         L.bf16 = bf16;
-        L.emu = sdpa_emu_setting();
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
         cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
@@ -473,6 +467,10 @@ int bdattn_sdpa_traced_fwd(const bdattn_sdpa_params* p, const bdattn_trace_param
     m.bias_ld = t->bias_ld > 0 ? t->bias_ld : t->bias_cols;
     m.map = t->attn_avg; m.map_row0 = t->map_row0; m.map_rows = t->map_rows; m.map_cols = t->map_cols;
     m.map_ld = t->map_ld > 0 ? t->map_ld : t->map_cols;
+    m.mask_mode = p->mask_mode;
+    m.q_offset = static_cast<int>(Lk - Lq);
+    m.key_mask = p->key_mask;
+    m.key_scale = p->key_scale;
     cudaError_t e = bdattn::launch_attn_map(m, p->dtype == BDATTN_BF16, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;
@@ -808,6 +806,9 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
     if (cached && (p->k_cached == nullptr || p->v_cached == nullptr || p->kv_rows < 1))
         return fail("%s: k_cached, v_cached and kv_rows must all be given", op);
     if (!cached && (p->wk == nullptr || p->wv == nullptr)) return fail("%s: wk and wv must not be null", op);
+    if (cached && (p->k_ld < C || p->v_ld < C || p->k_ld % 8 || p->v_ld % 8 || !aligned16(p->k_cached) ||
+                   !aligned16(p->v_cached)))
+        return fail("%s: cached K/V must be 16-byte aligned with ld >= inner_dim and a multiple of 8", op);
     const void* src = p->ctx != nullptr ? p->ctx : p->x;
     const int src_rows = p->ctx != nullptr ? p->ctx_rows : p->x_rows;
     const int src_cols = p->ctx != nullptr ? p->ctx_cols : p->x_cols;
@@ -852,8 +853,6 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
     const void* Vin = Vp;
     long long k_ld = ldp, v_ld = ldp;
     if (cached) {
-        if (p->k_ld < C || p->v_ld < C || p->k_ld % 8 || p->v_ld % 8 || !aligned16(p->k_cached) || !aligned16(p->v_cached))
-            return fail("%s: cached K/V must be 16-byte aligned with ld >= inner_dim and a multiple of 8", op);
         if (P != hd) {
             cudaError_t e = bdattn::launch_pad_heads(p->k_cached, Kp, Lk, nh, hd, P, p->k_ld, st);
             if (e == cudaSuccess) e = bdattn::launch_pad_heads(p->v_cached, Vp, Lk, nh, hd, P, p->v_ld, st);
@@ -886,7 +885,7 @@ int bdattn_qkvo_fwd(const bdattn_qkvo_params* p, bdattn_stream_t stream) {
         a.key_mask = p->key_mask;
         a.scale_log2 = scale * 1.4426950408889634f;
         L.q_ctas = a.q_ctas0;
-        L.num_heads = nh; L.batch = 1; L.head_dim = P; L.bf16 = bf16; L.emu = sdpa_emu_setting();
+        L.num_heads = nh; L.batch = 1; L.head_dim = P; L.bf16 = bf16;
         cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
     } else {

@@ -298,12 +298,12 @@ cudaError_t launch_gemm_tc05(const GemmLaunch& L, cudaStream_t stream) {
     dim3 grid(static_cast<unsigned>(tn), static_cast<unsigned>(tm), static_cast<unsigned>(L.n_problems));
     cudaError_t e;
     if (L.bf16) {
-        e = cudaFuncSetAttribute(gemm_tc05_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = set_max_smem_once(gemm_tc05_kernel<true>, 227 * 1024);
         if (e != cudaSuccess) return e;
         gemm_tc05_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
             L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], args);
     } else {
-        e = cudaFuncSetAttribute(gemm_tc05_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = set_max_smem_once(gemm_tc05_kernel<false>, 227 * 1024);
         if (e != cudaSuccess) return e;
         gemm_tc05_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(
             L.tmA[0], L.tmA[1], L.tmA[2], L.tmB[0], L.tmB[1], L.tmB[2], args);

@@ -393,19 +393,16 @@ int gemm_wide_tiles(const GemmLaunch& L) {
 
 cudaError_t launch_gemm_wide(const GemmLaunch& L, cudaStream_t stream) {
     const int total = gemm_wide_tiles(L);
-    int dev = 0, sms = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
+    const int sms = sm_count();
+    cudaError_t e;
     const int grid = total < sms ? total : sms;
     if (L.bf16) {
-        e = cudaFuncSetAttribute(gemm_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWSmemBytes);
+        e = set_max_smem_once(gemm_wide_kernel<true>, kWSmemBytes);
         if (e != cudaSuccess) return e;
         gemm_wide_kernel<true><<<grid, kWThreads, kWSmemBytes, stream>>>(
             L.tmA[0], L.tmA[1], L.tmA[2], L.tmBw[0], L.tmBw[1], L.tmBw[2], L.args, total);
     } else {
-        e = cudaFuncSetAttribute(gemm_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kWSmemBytes);
+        e = set_max_smem_once(gemm_wide_kernel<false>, kWSmemBytes);
         if (e != cudaSuccess) return e;
         gemm_wide_kernel<false><<<grid, kWThreads, kWSmemBytes, stream>>>(
             L.tmA[0], L.tmA[1], L.tmA[2], L.tmBw[0], L.tmBw[1], L.tmBw[2], L.args, total);
@@ -422,11 +419,7 @@ cudaError_t launch_gemm(const GemmLaunch& L, cudaStream_t stream) {
     bool wide = mode != 0 && L.n_problems > 0;
     for (int i = 0; i < L.n_problems; ++i) wide = wide && L.wide[i];
     if (wide) {
-        int dev = 0, sms = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-            sms = 148;
-        if (gemm_wide_tiles(L) >= sms) return launch_gemm_wide(L, stream);
+        if (gemm_wide_tiles(L) >= sm_count()) return launch_gemm_wide(L, stream);
     }
     return launch_gemm_tc05(L, stream);
 }

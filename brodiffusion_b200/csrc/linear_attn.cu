@@ -397,8 +397,10 @@ cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, 
                                const CUtensorMap& tmV, const CUtensorMap& tmO, int cluster_size,
                                cudaStream_t stream) {
     const size_t smem = sizeof(LaSmem) + static_cast<size_t>(a.stages - 1) * kLaSlotBytes + 1024;
-    cudaError_t e = cudaFuncSetAttribute(linear_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         static_cast<int>(smem));
+    // the larger of the two ring sizes is set once per device; both launches fit under it
+    constexpr int kMaxSmem = static_cast<int>(sizeof(LaSmem) + 7 * kLaSlotBytes + 1024);
+    if (static_cast<int>(smem) > kMaxSmem) return cudaErrorInvalidValue;
+    cudaError_t e = set_max_smem_once(linear_attn_kernel, kMaxSmem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(static_cast<unsigned>(cluster_size), static_cast<unsigned>(a.num_heads),

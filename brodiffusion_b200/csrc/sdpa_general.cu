@@ -161,13 +161,11 @@ cudaError_t launch_sdpa_general(const SdpaGeneralArgs& a, int num_heads, int bat
               static_cast<unsigned>(batch));
     cudaError_t e;
     if (bf16) {
-        e = cudaFuncSetAttribute(sdpa_general_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
+        e = set_max_smem_once(sdpa_general_kernel<true>, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         sdpa_general_kernel<true><<<grid, 128, smem, stream>>>(a, q_ctas0);
     } else {
-        e = cudaFuncSetAttribute(sdpa_general_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem));
+        e = set_max_smem_once(sdpa_general_kernel<false>, static_cast<int>(smem));
         if (e != cudaSuccess) return e;
         sdpa_general_kernel<false><<<grid, 128, smem, stream>>>(a, q_ctas0);
     }

@@ -56,7 +56,6 @@ struct SdpaLaunch {
     int batch;
     int head_dim;
     bool bf16;
-    int emu;   // exponentials per 8 evaluated by polynomial (0, 2, 4 or 6)
 };
 
 cudaError_t launch_sdpa_tc05(const SdpaLaunch& L, cudaStream_t stream);
@@ -99,6 +98,12 @@ struct AttnMapArgs {
     float* map;             // (map_rows, map_cols) FP32
     int map_row0, map_rows, map_cols;
     long long map_ld;
+    // The visibility rules the attention kernel applied, so that the map agrees
+    // with the output: a masked key has weight 0, a scaled key a scaled score.
+    int mask_mode;          // 1: key j visible to query i iff j <= i + q_offset
+    int q_offset;
+    const float* key_mask;  // Lk floats, 0 = masked; or null
+    const float* key_scale; // Lk floats or null
 };
 cudaError_t launch_attn_map(const AttnMapArgs& a, bool bf16, cudaStream_t stream);
 

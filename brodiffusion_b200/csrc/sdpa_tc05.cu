@@ -20,12 +20,13 @@
 // is carried by P and cancels in O / l), which makes the O rescale rare; the
 // rescale is done in tensor memory by the softmax warps themselves.
 //
-// The softmax is the co-bottleneck of this kernel (16 MUFU results per clock
-// per SM against 8192 dense BF16 FLOP per clock), so its arithmetic is packed
-// two floats per instruction (fma/add .f32x2), the row maximum uses the
-// three-input max, and a compile-time share of the exponentials is evaluated
-// on the FMA pipe with a degree-3 polynomial instead of ex2.approx (relative
-// error 1.0e-4, below the 2^-9 rounding of P to BF16).
+// What paces the kernel is the dependency chain of one query tile (scores ready
+// -> softmax -> P ready -> P.V and the next Q.K^T -> scores ready), of which the
+// softmax is the longest link, and the single MMA-issuing thread: tcgen05.mma
+// holds its issuing thread for as long as the MMA executes (64 cycles for
+// 128x128x16), so every wait, fence and commit of that thread is time the tensor
+// pipe idles.  The softmax arithmetic is therefore packed two floats per
+// instruction (fma/add .f32x2) and the row maximum uses the three-input max.
 //
 // Q, K and V are addressed through 4-D tensor maps (head element, head, row,
 // batch): a head narrower than the 64 / 128 columns the kernel computes with
@@ -113,39 +114,6 @@ __device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, 
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
-// round-towards-minus-infinity packed add (used to take floor(x) below)
-__device__ __forceinline__ void fadd2_rm(float& d0, float& d1, float a0, float a1, float b0, float b1) {
-    asm("{\n"
-        ".reg .b64 ra, rb, rd;\n"
-        "mov.b64 ra, {%2, %3};\n"
-        "mov.b64 rb, {%4, %5};\n"
-        "add.rm.f32x2 rd, ra, rb;\n"
-        "mov.b64 {%0, %1}, rd;\n"
-        "}\n"
-        : "=f"(d0), "=f"(d1)
-        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
-}
-// 2^x for two values on the FMA pipe: x = n + f with n = floor(x), f in [0,1);
-// 2^f by a degree-3 polynomial fitted on [0,1) with p(0) = 1 and p(1) = 2
-// (max relative error 1.03e-4), then n is added into the exponent field.
-// x is clamped to >= -127 (results below 2^-127 are zero for this purpose).
-__device__ __forceinline__ void exp2_poly2(float& p0, float& p1, float x0, float x1) {
-    constexpr float kMagic = 12582912.0f;  // 2^23 + 2^22: integers sit in the low mantissa bits
-    constexpr float kC1 = 0.6954243183135986f, kC2 = 0.2263076901435852f, kC3 = 0.07826796919107437f;
-    x0 = fmaxf(x0, -127.0f);
-    x1 = fmaxf(x1, -127.0f);
-    float r0, r1, b0, b1, f0, f1;
-    fadd2_rm(r0, r1, x0, x1, kMagic, kMagic);
-    fadd2(b0, b1, r0, r1, -kMagic, -kMagic);
-    fadd2(f0, f1, x0, x1, -b0, -b1);
-    float q0, q1;
-    ffma2(q0, q1, f0, f1, kC3, kC3, kC2, kC2);
-    ffma2(q0, q1, q0, q1, f0, f1, kC1, kC1);
-    ffma2(q0, q1, q0, q1, f0, f1, 1.0f, 1.0f);
-    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(r0) << 23));
-    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(r1) << 23));
-}
-
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
@@ -157,8 +125,7 @@ __device__ __forceinline__ void setmaxnreg_dec() {
 
 // HOOKS: 0 = none; 1 = key_mask only; 2 = key_mask, key_scale, val_scale, bias and the
 // per-row softmax statistics (slower softmax path).
-// EMU  : of every 8 consecutive exponentials, EMU are evaluated by polynomial.
-template <int HD, bool kBf16, int kHooks, int kEmu>
+template <int HD, bool kBf16, int kHooks>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                  const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
@@ -515,12 +482,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     const int c0 = ch * 32 + 2 * i;
                     float x0, x1, p0, p1;
                     ffma2(x0, x1, s[c0], s[c0 + 1], sl2, sl2, neg_ms, neg_ms);
-                    if ((i & 3) < kEmu / 2) {
-                        exp2_poly2(p0, p1, x0, x1);
-                    } else {
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
-                    }
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
                     fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
                     if constexpr (kHooks == 2) {
                         if (a.val_scale != nullptr) {
@@ -748,19 +711,12 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     }
 }
 
-template <int HD, bool kBf16, int kHooks, int kEmu>
+template <int HD, bool kBf16, int kHooks>
 cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     using C = Cfg<HD>;
-    auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks, kEmu>;
-    static thread_local int configured_dev = -1;
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (configured_dev != dev) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             C::kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured_dev = dev;
-    }
+    auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks>;
+    cudaError_t e = set_max_smem_once(kern, C::kSmemBytes);
+    if (e != cudaSuccess) return e;
     dim3 grid(static_cast<unsigned>(L.q_ctas), static_cast<unsigned>(L.num_heads),
               static_cast<unsigned>(L.batch));
     kern<<<grid, kThreads, C::kSmemBytes, stream>>>(L.tmQ[0], L.tmQ[1], L.tmK[0], L.tmK[1], L.tmV[0],
@@ -774,14 +730,9 @@ cudaError_t launch_hd(const SdpaLaunch& L, cudaStream_t stream) {
     // the other hooks' code; 0: none
     const bool all_hooks = L.args.key_scale != nullptr || L.args.val_scale != nullptr ||
                            L.args.bias != nullptr || L.args.lse != nullptr;
-    if (all_hooks) return launch_t<HD, kBf16, 2, 0>(L, stream);
-    if (L.args.key_mask != nullptr) return launch_t<HD, kBf16, 1, 0>(L, stream);
-    switch (L.emu) {
-        case 0: return launch_t<HD, kBf16, 0, 0>(L, stream);
-        case 2: return launch_t<HD, kBf16, 0, 2>(L, stream);
-        case 6: return launch_t<HD, kBf16, 0, 6>(L, stream);
-        default: return launch_t<HD, kBf16, 0, 4>(L, stream);
-    }
+    if (all_hooks) return launch_t<HD, kBf16, 2>(L, stream);
+    if (L.args.key_mask != nullptr) return launch_t<HD, kBf16, 1>(L, stream);
+    return launch_t<HD, kBf16, 0>(L, stream);
 }
 
 }  // namespace

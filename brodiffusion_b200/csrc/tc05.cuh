@@ -10,6 +10,8 @@
 #pragma once
 
 #include <cstdint>
+#include <mutex>
+#include <vector>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -26,6 +28,48 @@ enum : int {
 // library is built as a single translation unit, so this definition is the
 // only one.
 __device__ int g_device_status = 0;
+
+// ------------------------------------------------------------ host helpers
+// Raises a kernel's dynamic shared-memory limit to `bytes` once per (kernel,
+// device) instead of on every launch; a later request for more raises it again.
+inline cudaError_t set_max_smem_once_impl(const void* func, int bytes) {
+    struct Seen { const void* func; int dev; int bytes; };
+    static std::mutex mu;
+    static std::vector<Seen> seen;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    std::lock_guard<std::mutex> lock(mu);
+    for (Seen& s : seen) {
+        if (s.func == func && s.dev == dev) {
+            if (s.bytes >= bytes) return cudaSuccess;
+            e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+            if (e == cudaSuccess) s.bytes = bytes;
+            return e;
+        }
+    }
+    e = cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) seen.push_back({func, dev, bytes});
+    return e;
+}
+template <class Kernel>
+inline cudaError_t set_max_smem_once(Kernel kernel, int bytes) {
+    return set_max_smem_once_impl(reinterpret_cast<const void*>(kernel), bytes);
+}
+// Streaming-multiprocessor count of the current device, looked up once per device.
+inline int sm_count() {
+    static std::mutex mu;
+    static int count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    std::lock_guard<std::mutex> lock(mu);
+    if (count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        count[dev] = n;
+    }
+    return count[dev];
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));

@@ -374,6 +374,11 @@ int bdattn_project_kv(const void* ctx, int ctx_rows, int ctx_cols, long long ctx
  *     every byte it later reads (the projections also write the zero padding
  *     of the heads).  Two calls whose kernels overlap on the GPU (different
  *     streams, no ordering between them) race on the array: order them.
+ *   - The array's address is looked up once per device and kept for the life
+ *     of the process.  Do not use this entry point across cudaDeviceReset or
+ *     after the device's primary context has been destroyed and re-created:
+ *     the library's device image is reloaded then and the kept address is
+ *     stale.
  */
 size_t bdattn_qkvo_static_capacity(void);
 

@@ -49,6 +49,53 @@ inline void joint_attention(const bt::Tensor& Q, const bt::Tensor& K, const bt::
     bt::flash_attention_forward(Qr, Kr, V, /*d_mask=*/nullptr, num_heads, /*causal=*/false, out);
 }
 
+// src/dit/common.cpp:198-329 (include/brodiffusion/dit/common.h:117-129 of the
+// reference): joint_attention plus the head-averaged softmax map (L, L) in
+// attn_avg and an optional (img_len, txt_len) FP32 bias added to the scaled scores
+// of image-query rows [txt_len, L) x text-key columns [0, txt_len).  The
+// reference downloads Q/K/V and loops on the host; here everything stays on the
+// device.  attn_avg is FP32 (the reference stores it at the pipeline's compute
+// dtype; the callers only download it, src/dit/flux.cpp:505-508).
+inline void joint_attention_traced(const bt::Tensor& Q, const bt::Tensor& K, const bt::Tensor& V, const bt::Tensor& cos,
+                                   const bt::Tensor& sin, int head_dim, int num_heads, bt::Tensor& out,
+                                   bt::Tensor& attn_avg, bt::Tensor& Qr, bt::Tensor& Kr, int txt_len = 0,
+                                   const bt::Tensor* image_text_bias = nullptr) {
+    const int D = Q.cols, L = Q.rows;
+    if (head_dim <= 0 || num_heads <= 0 || D != head_dim * num_heads)
+        throw std::runtime_error("dit::common: joint_attention_traced: D must equal head_dim * num_heads");
+    if (K.rows != L || V.rows != L || K.cols != D || V.cols != D)
+        throw std::runtime_error("dit::common: joint_attention_traced: Q/K/V must share shape (L, D)");
+    if (image_text_bias != nullptr) {
+        if (txt_len < 0 || txt_len > L)
+            throw std::runtime_error("dit::common: joint_attention_traced: txt_len out of range for bias");
+        if (image_text_bias->dtype != bt::Dtype::FP32)
+            throw std::runtime_error("dit::common: joint_attention_traced: image_text_bias must be FP32");
+        if (image_text_bias->rows != L - txt_len || image_text_bias->cols != txt_len)
+            throw std::runtime_error("dit::common: joint_attention_traced: image_text_bias must be (img_len, txt_len)");
+    }
+    bt::rope_apply(Q, cos, sin, head_dim, num_heads, Qr);
+    bt::rope_apply(K, cos, sin, head_dim, num_heads, Kr);
+    out.resize(L, D, Q.dtype);
+    attn_avg.resize(L, L, bt::Dtype::FP32);
+    bt::Tensor ws;
+    ws.resize(1, static_cast<int>(bdattn_sdpa_traced_workspace_bytes(num_heads, L)), bt::Dtype::INT8);
+    bdattn_sdpa_params p{};
+    p.dtype = bt::detail::bd_dtype(Q.dtype);
+    p.batch = 1; p.num_heads = num_heads; p.head_dim = head_dim;
+    p.n_q_seg = 1; p.q[0] = Qr.data; p.o[0] = out.data; p.q_rows[0] = L; p.q_ld[0] = D; p.o_ld[0] = D;
+    p.n_kv_seg = 1; p.k[0] = Kr.data; p.v[0] = V.data; p.kv_rows[0] = L; p.k_ld[0] = D; p.v_ld[0] = D;
+    bdattn_trace_params t{};
+    if (image_text_bias != nullptr && txt_len > 0 && txt_len < L) {
+        t.bias = static_cast<const float*>(image_text_bias->data);
+        t.bias_row0 = txt_len; t.bias_rows = L - txt_len; t.bias_cols = txt_len; t.bias_ld = txt_len;
+    }
+    t.attn_avg = static_cast<float*>(attn_avg.data); t.map_rows = L; t.map_cols = L; t.map_ld = L;
+    t.workspace = ws.data; t.workspace_bytes = ws.bytes();
+    bt::detail::bd_check(bdattn_sdpa_traced_fwd(&p, &t, bt::detail::bd_stream()));
+    // the statistics scratch is freed when this returns: wait for the kernels that use it
+    bt::cuda_check(cudaStreamSynchronize(static_cast<cudaStream_t>(bt::cuda_current_stream())), "joint_attention_traced");
+}
+
 // src/dit/common.cpp:331-377 (Krea 2): grouped-query heads, optional RoPE,
 // optional key mask.  The kernel reads K/V head h / group for query head h, so
 // the widened copies the reference materialises (Krep / Vrep, common.cpp:361-375)

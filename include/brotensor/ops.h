@@ -132,6 +132,83 @@ inline void flash_attention_project_kv(const Tensor& ctx, const Tensor& Wk, cons
                                        detail::bd_dtype(ctx.dtype), detail::bd_stream()));
 }
 
+// src/dit/sana.cpp:441-443: C (batch, M, N) = A (batch, M, K) . B (batch, N, K)^T, the
+// "A . B^T" product Sana uses to project straight into the channel-major (D, N)
+// layout (A = W (D, D), B = x_mod (N, D), C = q (D, N); batch 1, strides 0).
+// strideA/B/C are the element distances between batch items.  The batched
+// calls inside the Sana attention core (sana.cpp:538-568) are replaced as a
+// whole by bdattn_linear_attn_relu_fwd; they still run here, one launch per
+// batch item.  The call sites on this path pass no bias (nullptr, 0).
+inline void matmul_abt(const Tensor& A, const Tensor& B, Tensor& C, int batch, int M, int N, int K,
+                       long long strideA, long long strideB, long long strideC, const Tensor* bias,
+                       int bias_mode) {
+    detail::require_gpu(A, "matmul_abt");
+    if (bias != nullptr || bias_mode != 0) throw std::runtime_error("matmul_abt: a bias is not supported");
+    if (A.dtype != B.dtype || (A.dtype != Dtype::BF16 && A.dtype != Dtype::FP16))
+        throw std::runtime_error("matmul_abt: operands must both be FP16 or both BF16");
+    if (batch < 1 || static_cast<long long>(A.size()) < (batch - 1) * strideA + static_cast<long long>(M) * K ||
+        static_cast<long long>(B.size()) < (batch - 1) * strideB + static_cast<long long>(N) * K)
+        throw std::runtime_error("matmul_abt: operand sizes do not cover batch x (M, K) and batch x (N, K)");
+    if (C.data == nullptr || static_cast<long long>(C.size()) < (batch - 1) * strideC + static_cast<long long>(M) * N ||
+        C.dtype != A.dtype)
+        C.resize(batch == 1 ? M : batch * M, N, A.dtype);
+    const std::size_t es = dtype_size(A.dtype);
+    for (int b = 0; b < batch; ++b) {
+        detail::bd_check(bdattn_linear_fwd(static_cast<const char*>(A.data) + b * strideA * es,
+                                           static_cast<const char*>(B.data) + b * strideB * es, nullptr,
+                                           static_cast<char*>(C.data) + b * strideC * es, detail::bd_dtype(A.dtype), M, N,
+                                           K, K, K, N, detail::bd_stream()));
+    }
+}
+
+// src/unet_blocks.cpp:282-290 (trace mode of the SD1.5 cross-attention): bias-free
+// Q/K/V projections, attention with an optional FP32 (Lq, Lk) logit bias added to
+// the scaled scores, bias-free output projection, and the head-averaged softmax
+// map (Lq, Lk) in AttnAvg (FP32).  The reference's operator recomputes the softmax
+// to expose it; here the attention kernel writes per-row statistics and a small
+// kernel evaluates the map from them (bdattn_sdpa_traced_fwd).
+inline void cross_attention_forward_with_attn(const Tensor& X, const Tensor& Ctx, const Tensor& Wq, const Tensor& Wk,
+                                              const Tensor& Wv, const Tensor& Wo, const float* d_mask,
+                                              const Tensor* attn_logit_bias, int num_heads, Tensor& Out,
+                                              Tensor& AttnAvg) {
+    detail::require_gpu(X, "cross_attention_forward_with_attn");
+    const int Lq = X.rows, Lk = Ctx.rows, inner = Wq.rows;
+    if (num_heads <= 0 || inner % num_heads != 0 || Wk.rows != inner || Wv.rows != inner || Wo.cols != inner ||
+        Wq.cols != X.cols || Wk.cols != Ctx.cols || Wv.cols != Ctx.cols)
+        throw std::runtime_error("cross_attention_forward_with_attn: weight shapes do not agree");
+    if (attn_logit_bias != nullptr &&
+        (attn_logit_bias->dtype != Dtype::FP32 || attn_logit_bias->rows != Lq || attn_logit_bias->cols != Lk))
+        throw std::runtime_error("cross_attention_forward_with_attn: attn_logit_bias must be FP32 (Lq, Lk)");
+    const int dt = detail::bd_dtype(X.dtype);
+    Tensor Q, K, V, O, ws;
+    Q.resize(Lq, inner, X.dtype); K.resize(Lk, inner, X.dtype); V.resize(Lk, inner, X.dtype); O.resize(Lq, inner, X.dtype);
+    detail::bd_check(bdattn_linear_fwd(X.data, Wq.data, nullptr, Q.data, dt, Lq, inner, X.cols, X.cols, Wq.cols, inner,
+                                       detail::bd_stream()));
+    detail::bd_check(bdattn_project_kv(Ctx.data, Lk, Ctx.cols, Ctx.cols, Wk.data, nullptr, Wv.data, nullptr, K.data,
+                                       V.data, inner, inner, dt, detail::bd_stream()));
+    AttnAvg.resize(Lq, Lk, Dtype::FP32);
+    const std::size_t need = bdattn_sdpa_traced_workspace_bytes(num_heads, Lq);
+    ws.resize(1, static_cast<int>(need), Dtype::INT8);
+    bdattn_sdpa_params p{};
+    p.dtype = dt; p.batch = 1; p.num_heads = num_heads; p.head_dim = inner / num_heads;
+    p.n_q_seg = 1; p.q[0] = Q.data; p.o[0] = O.data; p.q_rows[0] = Lq; p.q_ld[0] = inner; p.o_ld[0] = inner;
+    p.n_kv_seg = 1; p.k[0] = K.data; p.v[0] = V.data; p.kv_rows[0] = Lk; p.k_ld[0] = inner; p.v_ld[0] = inner;
+    p.key_mask = d_mask;
+    bdattn_trace_params t{};
+    if (attn_logit_bias != nullptr) {
+        t.bias = static_cast<const float*>(attn_logit_bias->data);
+        t.bias_rows = Lq; t.bias_cols = Lk; t.bias_ld = Lk;
+    }
+    t.attn_avg = static_cast<float*>(AttnAvg.data); t.map_rows = Lq; t.map_cols = Lk; t.map_ld = Lk;
+    t.workspace = ws.data; t.workspace_bytes = ws.bytes();
+    detail::bd_check(bdattn_sdpa_traced_fwd(&p, &t, detail::bd_stream()));
+    Out.resize(Lq, Wo.rows, X.dtype);
+    detail::bd_check(bdattn_linear_fwd(O.data, Wo.data, nullptr, Out.data, dt, Lq, Wo.rows, inner, inner, inner, Wo.rows,
+                                       detail::bd_stream()));
+    // the temporaries are freed when this returns: wait for the kernels that use them
+    cuda_check(cudaStreamSynchronize(static_cast<cudaStream_t>(cuda_current_stream())), "cross_attention_forward_with_attn");
+}
+
 // src/dit/qwenimage21_hooks.cpp:91-96 (QwenImage21PrefixCache::scale_kv)
 inline void scale_inplace(Tensor& Y, float a) {
     detail::require_gpu(Y, "scale_inplace");

@@ -8,6 +8,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstring>
 #include <random>
 #include <vector>
 
@@ -52,6 +53,7 @@ static bt::Tensor gpu_t(const std::vector<float>& v, int r, int c, bt::Dtype dt)
 static std::vector<float> download(const bt::Tensor& t) {
     const auto raw = t.to_host_bytes();
     std::vector<float> out(t.size());
+    if (t.dtype == bt::Dtype::FP32) { std::memcpy(out.data(), raw.data(), raw.size()); return out; }
     const auto* b = reinterpret_cast<const std::uint16_t*>(raw.data());
     for (std::size_t i = 0; i < out.size(); ++i) {
         if (t.dtype == bt::Dtype::BF16) out[i] = bt::bf16_bits_to_fp32(b[i]);
@@ -212,6 +214,90 @@ static void test_unet_attention() {
     expect_parity("cross-attn cached K/V", ref, download(out_c), 0.0f, 0.05f);
 }
 
+// dit::joint_attention_traced (src/dit/common.cpp:198-329): output, head-averaged
+// (L, L) map and the image->text logit bias, against the oracle's statement of the
+// same host loop.  Bounds: BF16 output 1e-2 (tests/test_flux_blocks.cpp:283-300);
+// map rows are non-negative and sum to one (tests/test_flux_blocks.cpp:268-281).
+static void test_joint_attention_traced(int txt, int hp, int wp, int nh, int hd, const std::vector<int>& axes, const char* label) {
+    const int L = txt + hp * wp, D = nh * hd, img = hp * wp;
+    const auto q = gen((std::size_t)L * D, 71, 1.0f, true), k = gen((std::size_t)L * D, 72, 1.0f, true),
+               v = gen((std::size_t)L * D, 73, 1.0f, true);
+    std::vector<float> bias((std::size_t)img * txt, 0.0f);
+    for (int r = 0; r < img; ++r) bias[(std::size_t)r * txt + 1] = 1.5f;     // steer every image row to text token 1
+    bd::dit::RopeTables tab = bd::dit::build_axial_rope_tables(txt, hp, wp, hd, axes);
+    bt::Tensor Q = gpu_t(q, L, D, bt::Dtype::BF16), K = gpu_t(k, L, D, bt::Dtype::BF16), V = gpu_t(v, L, D, bt::Dtype::BF16);
+    bt::Tensor B = bt::Tensor::from_host(bias.data(), img, txt);
+    bt::Tensor out, avg, out0, avg0, Qr, Kr;
+    bd::dit::joint_attention_traced(Q, K, V, tab.cos, tab.sin, hd, nh, out, avg, Qr, Kr, txt, &B);
+    bd::dit::joint_attention_traced(Q, K, V, tab.cos, tab.sin, hd, nh, out0, avg0, Qr, Kr);
+    std::vector<float> cos((std::size_t)L * hd / 2), sin(cos.size()), qr(q.size()), kr(k.size()), ref(q.size()),
+        ref_avg((std::size_t)L * L);
+    bdo_flux_rope_tables(txt, hp, wp, hd, axes.data(), (int)axes.size(), 10000.f, cos.data(), sin.data());
+    bdo_rope_apply(q.data(), L, nh, hd, cos.data(), sin.data(), 0, qr.data());
+    bdo_rope_apply(k.data(), L, nh, hd, cos.data(), sin.data(), 0, kr.data());
+    bdo_sdpa(qr.data(), L, kr.data(), v.data(), L, nh, hd, 0, nullptr, nullptr, nullptr, bias.data(), txt, txt, nullptr, L, 1, 0,
+             ref.data(), ref_avg.data());
+    expect_parity(label, ref, download(out), 0.0f, 1e-2f);
+    const auto m = download(avg), m0 = download(avg0);
+    expect_parity("  head-averaged map", ref_avg, m, 0.0f, 5e-3f);
+    float worst = 0.0f, steered = 0.0f, plain = 0.0f; bool neg = false;
+    for (int r = 0; r < L; ++r) {
+        float sum = 0.0f;
+        for (int c = 0; c < L; ++c) { sum += m[(std::size_t)r * L + c]; neg = neg || m[(std::size_t)r * L + c] < 0.0f; }
+        worst = std::max(worst, std::fabs(sum - 1.0f));
+        if (r >= txt) { steered += m[(std::size_t)r * L + 1]; plain += m0[(std::size_t)r * L + 1]; }
+    }
+    CHECK(!neg); CHECK(worst < 2e-2f);
+    CHECK(steered > plain);                 // the bias moves weight onto the steered text token
+    bool threw = false;
+    bt::Tensor bad = bt::Tensor::from_host(bias.data(), 1, txt);
+    try { bd::dit::joint_attention_traced(Q, K, V, tab.cos, tab.sin, hd, nh, out, avg, Qr, Kr, txt, &bad); }
+    catch (const std::runtime_error& e) { threw = std::string(e.what()).find("image_text_bias must be (img_len, txt_len)") != std::string::npos; }
+    CHECK(threw);
+}
+
+// brotensor::cross_attention_forward_with_attn (src/unet_blocks.cpp:282-290): the
+// traced SD1.5 cross-attention; the output bias is added afterwards by the caller.
+static void test_unet_traced_attention() {
+    const int L = 256, C = 320, nh = 8, Lc = 77, Cc = 768;
+    const auto x = gen((std::size_t)L * C, 81, 1.0f, false), ctx = gen((std::size_t)Lc * Cc, 82, 1.0f, false);
+    const auto wq = gen((std::size_t)C * C, 83, 0.05f, false), wo = gen((std::size_t)C * C, 84, 0.05f, false),
+               wk = gen((std::size_t)C * Cc, 85, 0.05f, false), wv = gen((std::size_t)C * Cc, 86, 0.05f, false),
+               lb = gen((std::size_t)L * Lc, 87, 0.5f, false);
+    bt::Tensor X = gpu_t(x, L, C, bt::Dtype::FP16), Ctx = gpu_t(ctx, Lc, Cc, bt::Dtype::FP16);
+    bt::Tensor Wq = gpu_t(wq, C, C, bt::Dtype::FP16), Wo = gpu_t(wo, C, C, bt::Dtype::FP16),
+               Wk = gpu_t(wk, C, Cc, bt::Dtype::FP16), Wv = gpu_t(wv, C, Cc, bt::Dtype::FP16);
+    bt::Tensor LB = bt::Tensor::from_host(lb.data(), L, Lc);
+    bt::Tensor out, avg;
+    bt::cross_attention_forward_with_attn(X, Ctx, Wq, Wk, Wv, Wo, nullptr, &LB, nh, out, avg);
+    std::vector<float> q((std::size_t)L * C), kk((std::size_t)Lc * C), vv(kk.size()), o(q.size()), ref(q.size()),
+        ref_avg((std::size_t)L * Lc);
+    bdo_linear(x.data(), wq.data(), nullptr, L, C, C, 0, q.data());
+    bdo_linear(ctx.data(), wk.data(), nullptr, Lc, C, Cc, 0, kk.data());
+    bdo_linear(ctx.data(), wv.data(), nullptr, Lc, C, Cc, 0, vv.data());
+    bdo_sdpa(q.data(), L, kk.data(), vv.data(), Lc, nh, C / nh, 0, nullptr, nullptr, nullptr, lb.data(), 0, Lc, nullptr, L, 1, 0,
+             o.data(), ref_avg.data());
+    bdo_linear(o.data(), wo.data(), nullptr, L, C, C, 0, ref.data());
+    expect_parity("traced cross-attn output", ref, download(out), 0.0f, 0.05f);   // tests/test_unet.cpp:379-409
+    const auto m = download(avg);
+    expect_parity("traced cross-attn map", ref_avg, m, 0.0f, 1e-2f);
+    float worst = 0.0f;
+    for (int r = 0; r < L; ++r) { float sum = 0.0f; for (int c = 0; c < Lc; ++c) sum += m[(std::size_t)r * Lc + c]; worst = std::max(worst, std::fabs(sum - 1.0f)); }
+    CHECK(worst < 0.05f);                                                          // tests/test_unet.cpp:487-500
+}
+
+// brotensor::matmul_abt as Sana calls it (src/dit/sana.cpp:441-443):
+// q (D, N) = W (D, D) . x_mod (N, D)^T, channel-major output, no bias.
+static void test_matmul_abt(int D, int N, const char* label) {
+    const auto w = gen((std::size_t)D * D, 91, 0.02f, true), x = gen((std::size_t)N * D, 92, 1.0f, true);
+    bt::Tensor W = gpu_t(w, D, D, bt::Dtype::BF16), X = gpu_t(x, N, D, bt::Dtype::BF16), Cm;
+    bt::matmul_abt(W, X, Cm, 1, D, N, D, 0, 0, 0, nullptr, 0);
+    CHECK(Cm.rows == D && Cm.cols == N);
+    std::vector<float> ref((std::size_t)D * N);
+    bdo_linear(w.data(), x.data(), nullptr, D, N, D, 0, ref.data());     // rows of W against rows of x_mod
+    expect_parity(label, ref, download(Cm), 0.01f, 0.004f);
+}
+
 static void test_refusals() {
     bt::Tensor cpu; cpu.device = bt::Device::cpu(); cpu.rows = 4; cpu.cols = 8; cpu.dtype = bt::Dtype::FP16;
     bt::Tensor y;
@@ -245,6 +331,10 @@ int main() {
         test_adds();
         test_prefix_cache_ops();
         test_unet_attention();
+        test_joint_attention_traced(3, 4, 4, 2, 8, {2, 2, 4}, "joint_attention_traced tiny (2x8)");   // tests/test_flux_blocks.cpp:480-507
+        test_joint_attention_traced(24, 12, 10, 4, 128, {16, 56, 56}, "joint_attention_traced 4x128");
+        test_unet_traced_attention();
+        test_matmul_abt(2240, 256, "matmul_abt Sana 2240 x 256 tokens");
         test_refusals();
         int status = 0;
         CHECK(bdattn_device_status(&status, 1) == 0 && status == 0);

@@ -4,7 +4,7 @@ import torch
 
 import synth
 
-MAX_ABS = 2e-2     # BASELINE tolerance: BF16 GPU vs FP32 CPU oracle
+MAX_ABS = 2e-2     # parity bound of the path: BF16 GPU vs FP32 CPU oracle
 MIN_COS = 0.9999
 
 

@@ -30,7 +30,7 @@ def test_golden(bd, golden):
 
 @pytest.mark.parametrize("N,B", [(1024, 2), (4096, 2), (1024, 1), (4096, 1)])
 def test_sana_1600m_shapes(bd, oracle, N, B):
-    """Config 4: 70 heads x 32, 1024 / 4096 tokens, batch 2 (CFG) and the
+    """Sana 1600M: 70 heads x 32, 1024 / 4096 tokens, batch 2 (CFG) and the
     reference's own per-branch batch of 1 (which runs as a cluster of 2)."""
     nh, hd = 70, 32
     D = nh * hd
@@ -45,6 +45,39 @@ def test_sana_1600m_shapes(bd, oracle, N, B):
         G.check(o, ref, what=f"sana N={N} b={b}")
         # after the (token-major) output projection: (N, D) @ Wo^T
         G.check(o.T[:256] @ wo.T, ref.T[:256] @ wo.T, what="sana after out-projection")
+
+
+@pytest.mark.parametrize("N", [1024, 4096])
+def test_sana_projections_feed_the_core_channel_major(bd, oracle, N):
+    """The three Sana projections at their real shape, q = W (2240, 2240) . x_mod (N, 2240)^T
+    -> (2240, N) channel-major, bias-free (src/dit/sana.cpp:441-443: matmul_abt with
+    W as the row operand), straight into the ReLU linear-attention core
+    (src/dit/sana.cpp:521-586)."""
+    nh, hd = 70, 32
+    D = nh * hd
+    x_mod = synth.activations((N, D), 6400 + N)
+    ws = [synth.weights((D, D), 6410 + i) for i in range(3)]
+    tx = G.dev(x_mod)
+    qkv = []
+    for w in ws:
+        y = torch.full((D, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+        bd.linear_fwd(G.dev(w), tx, None, y)          # rows of W against rows of x_mod
+        qkv.append(y)
+    assert bd.device_status() == 0
+    ref_qkv = [oracle.linear(w, x_mod) for w in ws]    # (D, N)
+    for name, y, r in zip("qkv", qkv, ref_qkv):
+        # reference bound for a 16-bit GEMM against FP32 (tests/test_fused_parity.cpp:66-90)
+        err = np.abs(G.host(y) - r).max()
+        assert err <= 0.01 * np.abs(r).max() + 0.004, f"{name} projection: {err}"
+    out = torch.full((D, N), float("nan"), device="cuda", dtype=torch.bfloat16)
+    bd.linear_attn_relu_fwd(qkv[0], qkv[1], qkv[2], out, nh, hd)
+    assert bd.device_status() == 0
+    # oracle on the device's own (BF16-rounded) projections: isolates the core ...
+    ref = oracle.sana_linear_attn(G.host(qkv[0]), G.host(qkv[1]), G.host(qkv[2]), nh, hd)
+    G.check(G.host(out), ref, what=f"sana core on projected q/k/v, N={N}")
+    # ... and end to end from x_mod with FP32 projections
+    ref_e2e = oracle.sana_linear_attn(ref_qkv[0], ref_qkv[1], ref_qkv[2], nh, hd)
+    G.check(G.host(out), ref_e2e, max_abs=3e-2, min_cos=0.999, what=f"sana projections + core, N={N}")
 
 
 @pytest.mark.parametrize("N", [8, 64, 120, 136, 520])

@@ -142,7 +142,7 @@ def test_qwen_prefill_as_segment_calls_equals_block_causal(oracle, golden):
 
 
 def test_four_text_blocks_of_64_equal_one_causal_run(oracle):
-    """Config 3 words the prefix as causal blocks of 64: four text segments of
+    """The Qwen-Image configuration words the prefix as causal blocks of 64: four text segments of
     64 are the same visibility rule as one text run of 256."""
     rng = np.random.default_rng(3)
     q, k, v = (rng.standard_normal((256, 2 * 16)).astype(np.float32) for _ in range(3))

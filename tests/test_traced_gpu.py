@@ -76,6 +76,37 @@ def test_unet_cross_attention_map(bd, oracle):
     assert np.abs(got.sum(1) - 1.0).max() < 0.05
 
 
+def test_map_agrees_with_masked_attention(bd, oracle):
+    """The map block follows the visibility rules the attention itself used: a
+    masked or future key has weight 0 and every visible row still sums to one."""
+    nh, hd, Lq, Lk = 4, 64, 200, 200
+    q, k, v = (synth.activations((Lq, nh * hd), 9300 + i) for i in range(3))
+    tq, tk, tv = G.dev(q), G.dev(k), G.dev(v)
+    # key mask (padded caption tail + a hole)
+    mask = np.ones(Lk, np.float32)
+    mask[150:] = 0.0
+    mask[7] = 0.0
+    out = torch.empty_like(tq)
+    amap = bd.sdpa_traced_fwd(tq, tk, tv, out, nh, map_rows=Lq, map_cols=Lk, key_mask=G.dev(mask, torch.float32))
+    assert bd.device_status() == 0
+    ref_out, ref_avg = oracle.sdpa(q, k, v, nh, key_mask=mask, want_avg=True)
+    G.check(G.host(out), ref_out, what="key-masked traced output")
+    m = G.host(amap)
+    assert np.abs(m - ref_avg).max() < 5e-3
+    assert np.all(m[:, mask == 0.0] == 0.0)
+    assert np.abs(m.sum(1) - 1.0).max() < 2e-2
+    # causal
+    out_c = torch.empty_like(tq)
+    amap_c = bd.sdpa_traced_fwd(tq, tk, tv, out_c, nh, map_rows=Lq, map_cols=Lk, mask_mode=bd.MASK_CAUSAL)
+    assert bd.device_status() == 0
+    ref_out_c, ref_avg_c = oracle.sdpa(q, k, v, nh, mask_mode=1, want_avg=True)
+    G.check(G.host(out_c), ref_out_c, what="causal traced output")
+    mc = G.host(amap_c)
+    assert np.abs(mc - ref_avg_c).max() < 5e-3
+    assert np.all(np.triu(mc, 1) == 0.0)
+    assert mc.max() <= 1.0 + 1e-3 and np.abs(mc.sum(1) - 1.0).max() < 2e-2
+
+
 def test_errors(bd):
     q = torch.zeros(64, 256, device="cuda", dtype=torch.bfloat16)
     b = torch.zeros(100, 10, device="cuda")

@@ -39,7 +39,7 @@ def test_golden_tiny_self_and_cross(bd, golden):
 
 @pytest.mark.parametrize("L,C,nh", [(4096, 320, 8), (1024, 640, 8), (256, 1280, 8), (64, 1280, 8)])
 def test_sd15_self_attention_levels(bd, oracle, L, C, nh):
-    """Config 1 and the deeper U-Net levels (src/unet.cpp:450): head dims 40,
+    """SD1.5 at 512 px and the deeper U-Net levels (src/unet.cpp:450): head dims 40,
     80 (padded to the tensor-core kernel) and 160 (general kernel)."""
     x = synth.activations((L, C), 7000 + L)
     wq, wk, wv, wo = (synth.weights((C, C), 7001 + L + i) for i in range(4))
@@ -152,3 +152,16 @@ def test_errors(bd):
     with pytest.raises(bd.BdattnError, match=r"^fused_linear_geglu: tensors must be FP16 or BF16"):
         xf = x.float()
         bd.linear_geglu_fwd(xf, xf, None, xf.clone())
+    # an output whose rows are narrower than what one row receives would be overwritten
+    y = torch.empty(16 * 320, device="cuda", dtype=torch.bfloat16).as_strided((16, 320), (160, 1))
+    with pytest.raises(bd.BdattnError, match=r"^bdattn_linear_fwd: output row stride 160 is smaller than the 320 columns"):
+        bd.linear_fwd(x, w, None, y)
+    # a bad cached K/V is refused before anything is enqueued: the output stays as it was
+    ws = torch.empty(bd.qkvo_workspace_bytes(16, 77, 8, 40), device="cuda", dtype=torch.uint8)
+    kc = torch.zeros(77, 324, device="cuda", dtype=torch.bfloat16)[:, 4:]      # rows start 8 bytes off a 16-byte boundary
+    out = torch.full((16, 320), 7.0, device="cuda", dtype=torch.bfloat16)
+    ws.zero_()
+    with pytest.raises(bd.BdattnError, match=r"^flash_attention_q_with_kv_cached_forward: cached K/V must be 16-byte aligned"):
+        bd.qkvo_fwd(x + 1, None, w + 1, None, None, w, None, 8, out, ws, k_cached=kc, v_cached=kc)
+    torch.cuda.synchronize()
+    assert bool((ws == 0).all()) and bool((out == 7.0).all())

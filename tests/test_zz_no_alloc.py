@@ -65,6 +65,26 @@ def test_static_scratch_matches_caller_scratch_on_two_calls_in_a_row(bd, oracle)
     G.check(again, got, what="repeat of call 1")
 
 
+def test_second_call_leaves_free_device_memory_unchanged(bd):
+    """What the name promises: once the first call on the device has looked up the
+    built-in array, a call changes the amount of free device memory by nothing.
+    Inputs, outputs and torch's caching allocator are set up before the
+    measurement; cudaMemGetInfo is read around the call itself."""
+    L, C, nh = 1024, 320, 8
+    x = torch.randn(L, C, device="cuda").bfloat16()
+    ws = [torch.randn(C, C, device="cuda").bfloat16() * 0.05 for _ in range(4)]
+    out = torch.empty(L, C, device="cuda", dtype=torch.bfloat16)
+    bd.qkvo_fwd(x, None, ws[0], ws[1], ws[2], ws[3], None, nh, out, None)      # first call: set-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        bd.qkvo_fwd(x, None, ws[0], ws[1], ws[2], ws[3], None, nh, out, None)
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert bd.device_status() == 0
+    assert free1 == free0, f"free device memory changed by {free0 - free1} bytes across calls"
+
+
 def test_shapes_beyond_the_built_in_scratch_are_refused(bd):
     L, C, nh = 16384, 320, 8
     assert bd.qkvo_workspace_bytes(L, L, nh, C // nh) > bd.qkvo_static_capacity()
