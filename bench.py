@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the denoiser-attention hot path.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--repeats R] [--impl ours|reference]
                   [--workload flux1024|flux2048_headsharded|sana1024|sana4096|flux1024_qkv_proj|flux1024_out_proj]
 
 One step = one pass of the hot path over one synthetic batch:
@@ -12,13 +12,29 @@ One step = one pass of the hot path over one synthetic batch:
                         fused the attention kernel normalises and rotates its own
                         query tiles and the pre-pass handles K only.
   flux2048_headsharded  (N GPUs) Flux.1 joint attention at 2048 px, batch 2,
-                        512 + 16384 tokens; heads split over the ranks, NCCL
-                        all-gather of the per-head outputs.  Default for N > 1.
+                        512 + 16384 tokens; heads split over the ranks, all-gather
+                        of the per-head outputs.  Default for N > 1.
   sana1024 / sana4096   (1 GPU)  Sana ReLU linear attention, batch 2 (GB/s).
   flux1024_qkv_proj / flux1024_out_proj  (1 GPU)  the projections either side of
                         the flux1024 attention call (projection TFLOP/s).
 The metric is attention TFLOP/s with the reference's own FLOP convention
 (4 * Lq * Lk * heads * head_dim, tools/bench_krea2_kernels.cpp:188-192).
+
+Timing: W warm-up steps, then the K-step region (barrier + synchronize on both
+sides, CUDA events on the launching stream, max over ranks) is measured R
+times; ``ms_per_step`` is the median region and the minimum and maximum are
+printed beside it.  SM clocks and throttle reasons are sampled across all R
+regions.
+
+The default one-GPU line also carries, measured in the same run after the
+timed regions: ``also`` (the other configurations of the path: Sana linear
+attention, the Qwen-Image cached step with and without the prefix scale
+vectors, the SD1.5 self-attention block, the Flux projections) and
+``library_baseline`` (torch SDPA and flash_attn on the same tensors).  A line
+for N > 1 carries ``gather_check`` (rank 0 recomputes heads another rank owns
+and compares them bit for bit with its gathered copy) and
+``one_gpu_same_workload`` (rank 0 alone on the whole call, for a like-for-like
+scaling figure).
 
 Prints ONE JSON line (rank 0).  ``--impl reference`` times the CPU restatement
 of the reference path (oracle/) on the host cores instead.
@@ -28,6 +44,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import statistics
 import sys
 import threading
 import time
@@ -43,8 +60,9 @@ WORKLOADS = {
     "flux1024": (1, 512, 64, 64),
     "flux2048_headsharded": (2, 512, 128, 128),
 }
-# Sana 1600M ReLU linear attention (config 4): name -> (batch, heads, tokens); 1 GPU, HBM-bound.
+# Sana 1600M ReLU linear attention: name -> (batch, heads, tokens); 1 GPU, HBM-bound.
 SANA_WORKLOADS = {"sana1024": (2, 70, 1024), "sana4096": (2, 70, 4096)}
+PROJ_WORKLOADS = {"flux1024_qkv_proj": 3, "flux1024_out_proj": 1}
 # dram__bytes_read.sum + dram__bytes_write.sum of one sdpa_tc05_kernel launch
 # on the flux1024 workload, from one ncu capture of that launch.
 NCU_TRAFFIC_BYTES = {"flux1024": 84.99e6 + 6.07e6}
@@ -72,7 +90,7 @@ def sustained_peak_tf():
 class ClockSampler:
     """Polls SM clock and throttle reasons through NVML (read-only)."""
 
-    def __init__(self, index: int, period_s: float = 0.005):
+    def __init__(self, index: int, period_s: float = 0.004):
         self.samples, self.reasons = [], set()
         self.max_mhz = None
         self._stop = threading.Event()
@@ -123,12 +141,34 @@ class ClockSampler:
 
     def summary(self):
         s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_min_mhz": s[0] if s else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s),
+                "sampled": "across the timed regions"}
 
 
 def attention_flops(batch, L):
     return 4.0 * batch * L * L * D
+
+
+def step_text(q_fused, world):
+    s = ("rmsnorm+rope of K -> joint softmax attention (rmsnorm+rope of Q inside)" if q_fused
+         else "rmsnorm+rope (Q,K) -> joint softmax attention")
+    return s + (" -> all-gather of head outputs" if world > 1 else "")
+
+
+def workload_config(args, world):
+    """The ``config`` object of the line: what is computed, identical for the GPU
+    arm and the host arm so that their lines describe the same job."""
+    batch, txt, hp, wp = WORKLOADS[args.workload]
+    L = txt + hp * wp
+    return {"workload": args.workload, "batch": batch, "tokens": L, "text_tokens": txt, "heads": NH,
+            "head_dim": HD, "heads_per_gpu": NH // world,
+            "step": step_text(args.q_norm == "fused", world),
+            "gather": "none" if world == 1 else
+                      ("fused peer stores in the attention epilogue + symmetric-memory barrier"
+                       if args.gather == "fused" else "nccl all-gather"),
+            "l2": "GPU arm: steps rotate over input sets that together exceed the 126 MB L2; "
+                  "host arm: inputs are read from host memory"}
 
 
 # ----------------------------------------------------------------- reference
@@ -162,22 +202,224 @@ def run_reference(args, rank, world):
     dt = (time.perf_counter() - t0) / args.steps
     tflops = 4.0 * rows_n * L * D / dt / 1e12
     sample = (f"{rows_n} of {L} query rows per step (all {NH} heads, all {L} keys), attention "
-              f"core in FP32, batch item 0; full-call time extrapolates to "
-              f"{batch * L / rows_n * dt * 1e3:.0f} ms")
+              f"core in FP32, batch item 0 of {batch}")
     line = {
         "impl": "reference", "metric": "attention TFLOP/s", "value": tflops, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": batch * L / rows_n * dt * 1e3, "higher_is_better": True,
+        "ms_per_step": dt * 1e3,                                       # one measured sample step
+        "full_call_ms_extrapolated": batch * L / rows_n * dt * 1e3,   # rows are independent
+        "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": args.workload, "batch": batch, "tokens": L, "heads": NH,
-                   "head_dim": HD},
+        "config": workload_config(args, max(1, args.gpus)),
         "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                          "sample": sample},
         "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0,
                 "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------ timing helpers
+def graph_ms(step, steps, reps=5, sampler=None):
+    """Median per-step device time of ``steps`` calls replayed from a CUDA graph
+    (host launch gaps do not enter the device time of microsecond kernels)."""
+    import torch
+    for i in range(3):
+        step(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                step(i)
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    if sampler is not None:
+        sampler.start()
+    out = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) / steps)
+    if sampler is not None:
+        t_end = time.perf_counter() + 0.2
+        while time.perf_counter() < t_end:        # keep the GPU busy while the clock sampler collects
+            graph.replay()
+        torch.cuda.synchronize()
+        sampler.stop()
+    return statistics.median(out)
+
+
+def measure_sana(bd, B, nh, N, steps=20, sampler=None):
+    """Sana linear attention: (ms, algorithmic GB/s).  Algorithmic bytes =
+    q, k, v read + out written = 4 * tokens * heads*32 * 2 bytes per batch item."""
+    import torch
+    Dm = nh * 32
+    byt = 4.0 * B * Dm * N * 2
+    n_sets = max(2, int(300e6 / byt) + 1)
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    sets = [tuple(torch.randn(B, Dm, N, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
+            for _ in range(n_sets)]
+    outs = [torch.empty(B, Dm, N, device="cuda", dtype=torch.bfloat16) for _ in range(n_sets)]
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        bd.linear_attn_relu_fwd(q, k, v, outs[i % n_sets], nh, 32)
+
+    ms = graph_ms(step, steps, sampler=sampler)
+    return ms, byt / (ms * 1e-3) / 1e9, n_sets, byt
+
+
+def measure_proj(bd, n_proj, steps=20, sampler=None):
+    """Projections around the Flux 1024 px attention call (4608 tokens, 3072 ->
+    3072, BF16): n_proj = 3 is one bdattn_qkv_norm_rope_fwd call, 1 is one
+    bdattn_linear_fwd call.  Returns (ms, TFLOP/s)."""
+    import torch
+    L, Dm, nh, hd = 4608, 3072, 24, 128
+    gen = torch.Generator(device="cuda").manual_seed(9876)
+    n_sets = 6                                   # 6 x 28 MB of activations > 126 MB L2
+    xs = [torch.randn(L, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(n_sets)]
+    W = [torch.randn(Dm, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) * 0.02 for _ in range(n_proj)]
+    outs = [torch.empty(L, Dm, device="cuda", dtype=torch.bfloat16) for _ in range(n_proj)]
+    gain = torch.ones(hd, device="cuda", dtype=torch.bfloat16)
+    cos, sin = bd.rope_tables_flux(512, 64, 64, hd)
+
+    def step(i):
+        x = xs[i % n_sets]
+        if n_proj == 3:
+            bd.qkv_norm_rope_fwd(x, W[0], W[1], W[2], outs[0], outs[1], outs[2], nh, hd, gain_q=gain, gain_k=gain,
+                                 cos=cos, sin=sin)
+        else:
+            bd.linear_fwd(x, W[0], None, outs[0])
+
+    ms = graph_ms(step, steps, sampler=sampler)
+    return ms, n_proj * 2.0 * L * Dm * Dm / (ms * 1e-3) / 1e12
+
+
+def measure_qwen_cached(bd, scaled, steps=10):
+    """Qwen-Image cached step: 4096 fresh query rows against a 256-row prefix K/V
+    cache (segment 0) plus the 4096 fresh rows, 24 x 128; ``scaled`` adds the
+    prefix K and V attenuation vectors.  Returns (ms, TFLOP/s)."""
+    import torch
+    P, T = 256, 4096
+    gen = torch.Generator(device="cuda").manual_seed(2468)
+    n_sets = 3                                   # 3 x (q + 2 x (P + T) rows) x 6 KB > 126 MB L2
+    sets = [(torch.randn(T, D, device="cuda", dtype=torch.bfloat16, generator=gen),
+             torch.randn(P + T, D, device="cuda", dtype=torch.bfloat16, generator=gen),
+             torch.randn(P + T, D, device="cuda", dtype=torch.bfloat16, generator=gen)) for _ in range(n_sets)]
+    out = torch.empty(T, D, device="cuda", dtype=torch.bfloat16)
+    kw = {}
+    if scaled:
+        ks = torch.ones(P + T, device="cuda")
+        vs = torch.ones(P + T, device="cuda")
+        ks[:P], vs[:P] = 0.5, 0.25
+        kw = dict(key_scale=ks, val_scale=vs)
+
+    def step(i):
+        q, k, v = sets[i % n_sets]
+        bd.sdpa_fwd(q, [k[:P], k[P:]], [v[:P], v[P:]], out, NH, **kw)
+
+    ms = graph_ms(step, steps)
+    return ms, 4.0 * T * (P + T) * D / (ms * 1e-3) / 1e12
+
+
+def measure_sd15_block(bd, steps=20):
+    """SD1.5 self-attention block at 512 px (one CFG branch): x (4096, 320), 8 heads x
+    40, Q/K/V projections + attention + output projection in one bdattn_qkvo_fwd
+    call.  Returns (ms, TFLOP/s over core + projection FLOP)."""
+    import torch
+    L, C, nh = 4096, 320, 8
+    gen = torch.Generator(device="cuda").manual_seed(1357)
+    n_sets = 56                                  # 56 x 2.6 MB activations > 126 MB L2
+    xs = [torch.randn(L, C, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(n_sets)]
+    ws = [torch.randn(C, C, device="cuda", dtype=torch.bfloat16, generator=gen) * 0.05 for _ in range(4)]
+    bo = torch.zeros(C, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(L, C, device="cuda", dtype=torch.bfloat16)
+    wsp = torch.empty(bd.qkvo_workspace_bytes(L, L, nh, C // nh), device="cuda", dtype=torch.uint8)
+
+    def step(i):
+        bd.qkvo_fwd(xs[i % n_sets], None, ws[0], ws[1], ws[2], ws[3], bo, nh, out, wsp)
+
+    ms = graph_ms(step, steps)
+    flop = 4.0 * L * L * C + 4 * 2.0 * L * C * C
+    return ms, flop / (ms * 1e-3) / 1e12
+
+
+def other_configurations(bd):
+    """The ``also`` block: the remaining configurations of the path, each timed
+    for a few milliseconds in this same process."""
+    peak_tf, peak_gbs, kind = measured_peaks()
+    also = {"peaks": f"{kind}: {peak_tf} TFLOP/s BF16 burst, {peak_gbs} GB/s copy",
+            "timing": "CUDA-graph replay, median of 5, inputs rotate over sets larger than L2"}
+
+    def tensor(name, fn, what):
+        try:
+            ms, tf = fn()
+            also[name] = {"ms": ms, "achieved": tf, "unit": "TFLOP/s", "frac": tf / peak_tf, "what": what}
+        except Exception as e:          # a configuration that fails is reported, not hidden
+            also[name] = {"error": f"{type(e).__name__}: {e}"}
+
+    for name, (B, nh, N) in SANA_WORKLOADS.items():
+        try:
+            ms, gbs, _, _ = measure_sana(bd, B, nh, N)
+            also[name] = {"ms": ms, "achieved": gbs, "unit": "GB/s", "frac": gbs / peak_gbs,
+                          "what": f"Sana ReLU linear attention, batch {B}, {nh} x 32, {N} tokens"}
+        except Exception as e:
+            also[name] = {"error": f"{type(e).__name__}: {e}"}
+    tensor("qwen_cached", lambda: measure_qwen_cached(bd, False),
+           "Qwen-Image cached step, 4096 queries x (256 cached + 4096) keys, 24 x 128")
+    tensor("qwen_cached_scaled", lambda: measure_qwen_cached(bd, True),
+           "same with the prefix K and V scale vectors")
+    tensor("sd15_self_block", lambda: measure_sd15_block(bd),
+           "SD1.5 self-attention block 4096 x 320, 8 x 40: projections + attention + out-projection")
+    tensor("flux1024_qkv_proj", lambda: measure_proj(bd, 3),
+           "Q/K/V projections 4608 x 3072 -> 3 x 3072 with RMSNorm + RoPE in the epilogue")
+    tensor("flux1024_out_proj", lambda: measure_proj(bd, 1), "output projection 4608 x 3072 x 3072")
+    return also
+
+
+def library_baselines(sets, batch, L, nh_l):
+    """torch SDPA and flash_attn on the tensors of the timed workload (library
+    kernels on the same box; context, not part of the product path)."""
+    import torch
+    res = {"what": "attention core only on the workload's tensors, median of 10, CUDA events"}
+    flops = 4.0 * batch * L * L * nh_l * HD
+
+    def timed(fn):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        ts = []
+        for i in range(10):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    try:
+        import torch.nn.functional as F
+        views = [tuple(t.view(batch, L, nh_l, HD).transpose(1, 2) for t in s) for s in sets]
+        ms = timed(lambda i: F.scaled_dot_product_attention(*views[i % len(views)]))
+        res["torch_sdpa"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    except Exception as e:
+        res["torch_sdpa"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+    try:
+        from flash_attn import flash_attn_func
+        views = [tuple(t.view(batch, L, nh_l, HD) for t in s) for s in sets]
+        ms = timed(lambda i: flash_attn_func(*views[i % len(views)]))
+        res["flash_attn"] = {"ms": ms, "tflops": flops / (ms * 1e-3) / 1e12}
+    except Exception as e:
+        res["flash_attn"] = {"error": f"{type(e).__name__}: {e}"[:200]}
+    return res
 
 
 # ---------------------------------------------------------------------- ours
@@ -205,29 +447,28 @@ def run_ours(args, rank, world, local_rank):
     cos, sin = bd.rope_tables_flux(txt, hp, wp, HD, device=dev)
     gains = [torch.from_numpy(synth.gains(HD, 20 + i)).to(dev).bfloat16() for i in range(4)]
 
+    def make_sets(seed, width, count):
+        gen = torch.Generator(device=dev).manual_seed(seed)
+        return [tuple(torch.randn(batch, L, width, device=dev, dtype=torch.bfloat16, generator=gen)
+                      for _ in range(3)) for _ in range(count)]
+
     # Rotating input sets so that consecutive steps do not find their inputs in L2.
     set_bytes = 3 * batch * L * d_l * 2
     n_sets = max(2, int(np.ceil(160e6 / set_bytes)) + 1)
-    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
-    sets = []
-    for _ in range(n_sets):
-        sets.append(tuple(torch.randn(batch, L, d_l, device=dev, dtype=torch.bfloat16, generator=gen)
-                          for _ in range(3)))
+    sets = make_sets(1234 + rank, d_l, n_sets)
     kr = torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16)
     # N > 1: the head outputs are gathered either by the attention kernel itself
     # (epilogue stores into every rank's replica through symmetric memory) or,
     # with --gather nccl, by an in-place NCCL all-gather of a head-major staging tensor.
-    gathered, peer_ptrs, gather_mode = None, None, "none"
+    gathered, peer_ptrs = None, None
+    config = workload_config(args, world)
     if world > 1 and args.gather == "fused":
         try:
             gathered = headshard.GatheredOutput(batch, L, NH, HD, torch.bfloat16, dev)
             peer_ptrs = [gathered.peer_ptrs(0), gathered.peer_ptrs(txt)]
-            gather_mode = "fused peer stores in the attention epilogue + symmetric-memory barrier"
         except Exception as e:      # symmetric memory unavailable: NCCL path
             gathered = None
-            gather_mode = f"nccl (symmetric memory unavailable: {type(e).__name__})"
-    elif world > 1:
-        gather_mode = "nccl all-gather"
+            config["gather"] = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
     staging = torch.empty(headshard.staging_shape(world, batch, L, NH, HD), device=dev,
                           dtype=torch.bfloat16)
     out = gathered.local if gathered is not None else staging[rank]
@@ -238,23 +479,28 @@ def run_ours(args, rank, world, local_rank):
     q_fused = args.q_norm == "fused"
     qr = None if q_fused else torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16)
 
-    def norm_rope(q, k):
+    def norm_rope(q, k, kr_=None, qr_=None, heads=None):
+        kr_ = kr if kr_ is None else kr_
+        qr_ = qr if qr_ is None else qr_
         for b in range(batch):
             jobs = [
-                dict(x=k[b, :txt], out=kr[b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
-                dict(x=k[b, txt:], out=kr[b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
+                dict(x=k[b, :txt], out=kr_[b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
+                dict(x=k[b, txt:], out=kr_[b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
             ]
             if not q_fused:
-                jobs += [dict(x=q[b, :txt], out=qr[b, :txt], gain=gains[2], cos=cos, sin=sin, rope_row0=0),
-                         dict(x=q[b, txt:], out=qr[b, txt:], gain=gains[0], cos=cos, sin=sin, rope_row0=txt)]
-            bd.rmsnorm_rope(jobs, nh_l, HD)
+                jobs += [dict(x=q[b, :txt], out=qr_[b, :txt], gain=gains[2], cos=cos, sin=sin, rope_row0=0),
+                         dict(x=q[b, txt:], out=qr_[b, txt:], gain=gains[0], cos=cos, sin=sin, rope_row0=txt)]
+            bd.rmsnorm_rope(jobs, nh_l if heads is None else heads, HD)
 
     q_norm = dict(gain=[gains[2], gains[0]], cos=cos, sin=sin, rope_row0=0) if q_fused else {}
 
-    def attention(q, v):
-        qq = q if q_fused else qr
-        bd.sdpa_fwd([qq[:, :txt], qq[:, txt:]], [kr[:, :txt], kr[:, txt:]], [v[:, :txt], v[:, txt:]],
-                    [out[:, :txt], out[:, txt:]], nh_l, q_norm=q_norm, peer_out_ptrs=peer_ptrs)
+    def attention(q, v, out_=None, kr_=None, qr_=None, heads=None, peers=True):
+        out_ = out if out_ is None else out_
+        kr_ = kr if kr_ is None else kr_
+        qq = q if q_fused else (qr if qr_ is None else qr_)
+        bd.sdpa_fwd([qq[:, :txt], qq[:, txt:]], [kr_[:, :txt], kr_[:, txt:]], [v[:, :txt], v[:, txt:]],
+                    [out_[:, :txt], out_[:, txt:]], nh_l if heads is None else heads, q_norm=q_norm,
+                    peer_out_ptrs=peer_ptrs if peers else None)
 
     def gather():
         if gathered is not None:
@@ -307,32 +553,26 @@ def run_ours(args, rank, world, local_rank):
     q_norm.update(qn_saved)
     barrier()
 
+    # ------------------------------------------------------- the timed regions
     sampler = ClockSampler(local_rank)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    region_ms = []
     barrier()
     sampler.start()
-    e0.record()
-    for i in range(args.steps):
-        step(i)
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1) / args.steps
-    if len(sampler.samples) < 5:
-        # the timed region was shorter than a few sampling periods: keep
-        # sampling over ~0.5 s of the same steps (untimed)
-        t_end = time.perf_counter() + 0.5
-        i = 0
-        while time.perf_counter() < t_end:
+    for _ in range(args.repeats):
+        barrier()
+        e0.record()
+        for i in range(args.steps):
             step(i)
-            i += 1
-            if i % 8 == 0:
-                torch.cuda.synchronize()
-        torch.cuda.synchronize()
+        e1.record()
+        barrier()
+        region_ms.append(e0.elapsed_time(e1) / args.steps)
     sampler.stop()
     if world > 1:
-        t = torch.tensor([ms], device=dev)
+        t = torch.tensor(region_ms, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        region_ms = [float(x) for x in t.tolist()]
+    ms = statistics.median(region_ms)
     if bd.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure during the timed region")
 
@@ -346,86 +586,144 @@ def run_ours(args, rank, world, local_rank):
     achieved = local_flops / (kernel_ms * 1e-3) / 1e12
     achieved_sustained = local_flops / (kernel_ms_sustained * 1e-3) / 1e12
 
-    # end to end: host buffers in, result back to the host, every step
+    # ------------------------------------------------ N > 1: gather check, 1-GPU figure
+    gather_check, one_gpu = None, None
+    if world > 1:
+        # One more step on set 0, then rank 0 recomputes the heads rank 1 owns from
+        # rank 1's own inputs (regenerated from its seed) with the plain, unsharded
+        # launch and compares them bit for bit with its gathered copy.
+        step(0)
+        barrier()
+        if rank == 0:
+            oq, ok_, ov = make_sets(1234 + 1, d_l, 1)[0]
+            o_kr, o_qr = torch.empty_like(ok_), (None if q_fused else torch.empty_like(oq))
+            o_out = torch.empty_like(oq)
+            norm_rope(oq, ok_, kr_=o_kr, qr_=o_qr)
+            attention(oq, ov, out_=o_out, kr_=o_kr, qr_=o_qr, peers=False)
+            torch.cuda.synchronize()
+            c0 = headshard.head_range(NH, world, 1)[0] * HD
+            theirs = gathered.full[:, :, c0:c0 + d_l] if gathered is not None else staging[1]
+            gather_check = "bit-exact" if torch.equal(theirs, o_out) else "mismatch"
+            del oq, ok_, ov, o_kr, o_qr, o_out
+        barrier()
+        # rank 0 alone on the whole call (all 24 heads, no gather), for a like-for-like
+        # scaling figure; the other ranks wait at the barrier
+        if rank == 0:
+            f_sets = make_sets(4321, D, 2)
+            f_kr = torch.empty(batch, L, D, device=dev, dtype=torch.bfloat16)
+            f_qr = None if q_fused else torch.empty_like(f_kr)
+            f_out = torch.empty_like(f_kr)
+
+            def full_step(i):
+                fq, fk, fv = f_sets[i % 2]
+                norm_rope(fq, fk, kr_=f_kr, qr_=f_qr, heads=NH)
+                attention(fq, fv, out_=f_out, kr_=f_kr, qr_=f_qr, heads=NH, peers=False)
+
+            for i in range(3):
+                full_step(i)
+            torch.cuda.synchronize()
+            n1 = 10
+            e0.record()
+            for i in range(n1):
+                full_step(i)
+            e1.record()
+            torch.cuda.synchronize()
+            ms1 = e0.elapsed_time(e1) / n1
+            v1 = flops / (ms1 * 1e-3) / 1e12
+            one_gpu = {"ms_per_step": ms1, "value": v1, "unit": "TFLOP/s", "steps": n1,
+                       "what": "rank 0 alone: all 24 heads of the same call, no gather, other ranks idle",
+                       "efficiency_vs_it": (flops / (ms * 1e-3) / 1e12) / (world * v1)}
+            del f_sets, f_kr, f_qr, f_out
+        barrier()
+
+    # ------------------------------------------------------------ end to end
+    # host buffers in, result back to the host, every step
     hq, hk, hv = (torch.randn(batch, L, d_l, dtype=torch.bfloat16).pin_memory() for _ in range(3))
     ho = torch.empty(batch, L, d_l, dtype=torch.bfloat16).pin_memory()
-    dq, dk, dv = (torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    # K and V go up first, then the query rows in chunks; each chunk is normalised,
+    # rotated and attended as soon as it has arrived (query rows are independent), and
+    # its output rows go back to the host while the next chunk is computed, so the two
+    # PCIe directions and the kernels overlap.  Two sets of device buffers alternate so
+    # that step i+1 can start uploading while step i drains.  With N > 1 every rank
+    # runs this pipeline on its own heads; the chunks of one step share one cross-GPU
+    # barrier after the last chunk (fused gather) or one NCCL all-gather.
+    e2e_mode = "pipelined: K/V upload, then query-row chunks over upload / compute / download streams"
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def buf():
+        return torch.empty(batch, L, d_l, device=dev, dtype=torch.bfloat16)
+
+    bufs = [dict(q=buf(), k=buf(), v=buf(), kr=buf(), done=None, drained=None) for _ in range(2)]
+    for Bf in bufs:
+        Bf["o"] = out if world > 1 else buf()
+        Bf["od"] = buf() if world > 1 else None
+    img = L - txt
+    n_img_chunks = 4 if img % 4 == 0 and (img // 4) % 256 == 0 else 1
+    chunks = [(0, txt)] + [(txt + c * (img // n_img_chunks), txt + (c + 1) * (img // n_img_chunks))
+                           for c in range(n_img_chunks)]
+    step_no = [0]
 
     def e2e_step():
-        dq.copy_(hq, non_blocking=True)
-        dk.copy_(hk, non_blocking=True)
-        dv.copy_(hv, non_blocking=True)
-        norm_rope(dq, dk)
-        attention(dq, dv)
+        Bf = bufs[step_no[0] % 2]
+        step_no[0] += 1
+        cur = torch.cuda.current_stream(dev)
+        if Bf["done"] is not None:
+            s_in.wait_event(Bf["done"])        # the kernels that read this buffer set two steps ago
+        with torch.cuda.stream(s_in):
+            Bf["k"].copy_(hk, non_blocking=True)
+            Bf["v"].copy_(hv, non_blocking=True)
+            ev_kv = torch.cuda.Event()
+            ev_kv.record(s_in)
+            ev_q = []
+            for r0, r1 in chunks:
+                for b in range(batch):             # one contiguous slab per copy
+                    Bf["q"][b, r0:r1].copy_(hq[b, r0:r1], non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(s_in)
+                ev_q.append(e)
+        cur.wait_event(ev_kv)
+        # this set's output buffer has reached the host (with N > 1 both sets write
+        # the one gathered output, so the previous step's download is the one to wait for)
+        prev = bufs[(step_no[0]) % 2]["drained"] if world > 1 else Bf["drained"]
+        for ev in (Bf["drained"], prev):
+            if ev is not None:
+                cur.wait_event(ev)
+        for b in range(batch):
+            bd.rmsnorm_rope([
+                dict(x=Bf["k"][b, :txt], out=Bf["kr"][b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
+                dict(x=Bf["k"][b, txt:], out=Bf["kr"][b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
+            ], nh_l, HD)
+        for ci, (r0, r1) in enumerate(chunks):
+            cur.wait_event(ev_q[ci])
+            pp = None
+            if gathered is not None:
+                pp = [gathered.peer_ptrs(r0)]
+            bd.sdpa_fwd(Bf["q"][:, r0:r1], [Bf["kr"][:, :txt], Bf["kr"][:, txt:]],
+                        [Bf["v"][:, :txt], Bf["v"][:, txt:]], Bf["o"][:, r0:r1], nh_l,
+                        q_norm=dict(gain=gains[2] if r0 < txt else gains[0], cos=cos, sin=sin, rope_row0=r0),
+                        peer_out_ptrs=pp)
+            ev_o = torch.cuda.Event()
+            ev_o.record(cur)
+            s_out.wait_event(ev_o)
+            with torch.cuda.stream(s_out):
+                for b in range(batch):
+                    if world == 1:
+                        ho[b, r0:r1].copy_(Bf["o"][b, r0:r1], non_blocking=True)
+                    else:
+                        # rows of the gathered output are D wide: gather this rank's head
+                        # columns into a dense slab first, then one contiguous download
+                        Bf["od"][b, r0:r1].copy_(Bf["o"][b, r0:r1], non_blocking=True)
+                        ho[b, r0:r1].copy_(Bf["od"][b, r0:r1], non_blocking=True)
         gather()
-        ho.copy_(out, non_blocking=True)
+        Bf["done"] = torch.cuda.Event()
+        Bf["done"].record(cur)
+        Bf["drained"] = torch.cuda.Event()
+        Bf["drained"].record(s_out)
 
-    # One GPU: the same work as a pipeline over three streams.  K and V go up
-    # first, then the query rows in chunks; each chunk is normalised, rotated and
-    # attended as soon as it has arrived (query rows are independent), and its
-    # output rows go back to the host while the next chunk is computed, so the
-    # two PCIe directions and the kernels overlap.  Two sets of device buffers
-    # alternate so that step i+1 can start uploading while step i drains.
-    e2e_mode = "serial copies and kernels on one stream"
-    if world == 1:
-        e2e_mode = "pipelined: K/V upload, then query-row chunks over upload / compute / download streams"
-        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        bufs = [dict(q=torch.empty_like(dq), k=torch.empty_like(dq), v=torch.empty_like(dq),
-                     kr=torch.empty_like(dq), o=torch.empty_like(dq),
-                     done=None, drained=None) for _ in range(2)]
-        img = L - txt
-        n_img_chunks = 4 if img % 4 == 0 and (img // 4) % 256 == 0 else 1
-        chunks = [(0, txt)] + [(txt + c * (img // n_img_chunks), txt + (c + 1) * (img // n_img_chunks))
-                               for c in range(n_img_chunks)]
-        step_no = [0]
-
-        def e2e_step():
-            B = bufs[step_no[0] % 2]
-            step_no[0] += 1
-            cur = torch.cuda.current_stream(dev)
-            if B["done"] is not None:
-                s_in.wait_event(B["done"])        # the kernels that read this buffer set two steps ago
-            with torch.cuda.stream(s_in):
-                B["k"].copy_(hk, non_blocking=True)
-                B["v"].copy_(hv, non_blocking=True)
-                ev_kv = torch.cuda.Event()
-                ev_kv.record(s_in)
-                ev_q = []
-                for r0, r1 in chunks:
-                    B["q"][:, r0:r1].copy_(hq[:, r0:r1], non_blocking=True)
-                    e = torch.cuda.Event()
-                    e.record(s_in)
-                    ev_q.append(e)
-            cur.wait_event(ev_kv)
-            if B["drained"] is not None:
-                cur.wait_event(B["drained"])      # this set's output has reached the host
-            for b in range(batch):
-                bd.rmsnorm_rope([
-                    dict(x=B["k"][b, :txt], out=B["kr"][b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
-                    dict(x=B["k"][b, txt:], out=B["kr"][b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
-                ], nh_l, HD)
-            for ci, (r0, r1) in enumerate(chunks):
-                cur.wait_event(ev_q[ci])
-                bd.sdpa_fwd(B["q"][:, r0:r1], [B["kr"][:, :txt], B["kr"][:, txt:]],
-                            [B["v"][:, :txt], B["v"][:, txt:]], B["o"][:, r0:r1], nh_l,
-                            q_norm=dict(gain=gains[2] if r0 < txt else gains[0], cos=cos, sin=sin, rope_row0=r0))
-                ev_o = torch.cuda.Event()
-                ev_o.record(cur)
-                s_out.wait_event(ev_o)
-                with torch.cuda.stream(s_out):
-                    ho[:, r0:r1].copy_(B["o"][:, r0:r1], non_blocking=True)
-            B["done"] = torch.cuda.Event()
-            B["done"].record(cur)
-            B["drained"] = torch.cuda.Event()
-            B["drained"].record(s_out)
-
-        def e2e_join():
-            cur = torch.cuda.current_stream(dev)
-            cur.wait_stream(s_in)
-            cur.wait_stream(s_out)
-    else:
-        def e2e_join():
-            pass
+    def e2e_join():
+        cur = torch.cuda.current_stream(dev)
+        cur.wait_stream(s_in)
+        cur.wait_stream(s_out)
 
     e2e_steps = max(3, min(args.steps, 10))
     for _ in range(2):
@@ -443,27 +741,24 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+    if bd.device_status() != 0:
+        raise RuntimeError("a kernel reported a device-side failure during the end-to-end region")
 
-    line = None
     if rank == 0:
-        clocks = sampler.summary()
         line = {
             "metric": "attention TFLOP/s", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "repeats": args.repeats,
+            "ms_per_step": ms, "ms_per_step_min": min(region_ms), "ms_per_step_max": max(region_ms),
             "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "batch": batch, "tokens": L, "text_tokens": txt,
-                       "heads": NH, "head_dim": HD, "heads_per_gpu": nh_l,
-                       "step": ("rmsnorm+rope of K -> joint softmax attention (rmsnorm+rope of Q inside)" if q_fused else "rmsnorm+rope (Q,K) -> joint softmax attention") +
-                               (" -> all-gather of head outputs" if world > 1 else ""),
-                       "gather": gather_mode,
-                       "l2": f"rotating {n_sets} input sets ({n_sets * set_bytes / 1e6:.0f} MB > 126 MB L2)"},
-            "clocks": clocks,
+            "config": config,
+            "l2_sets": f"{n_sets} input sets, {n_sets * set_bytes / 1e6:.0f} MB per rank",
+            "clocks": sampler.summary(),
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms, "mode": e2e_mode,
                     "h2d_bytes_per_step": 3 * batch * L * d_l * 2,
                     "d2h_bytes_per_step": batch * L * d_l * 2},
-            "gpu_launches": launches_per_step * args.steps,
+            "gpu_launches": launches_per_step * args.steps * args.repeats,
             "roofline": {"bound": "tensor", "kernel": "sdpa_tc05_kernel", "achieved": achieved,
                          "peak": peak_tf, "unit": "TFLOP/s", "frac": achieved / peak_tf,
                          "peak_kind": f"{peak_kind} cuBLAS bf16 burst", "kernel_ms": kernel_ms,
@@ -472,8 +767,8 @@ def run_ours(args, rank, world, local_rank):
                          # against the burst cuBLAS figure; *_sustained: timed again in a
                          # back-to-back loop after it, against the sustained cuBLAS figure
                          "achieved_sustained": achieved_sustained, "kernel_ms_sustained": kernel_ms_sustained,
-                         # the launch above normalises and rotates its query tiles first;
-                         # *_plain is the same kernel given pre-normalised queries
+                         # with --q-norm fused the launch above normalises and rotates its
+                         # query tiles first; *_plain is the kernel given pre-normalised queries
                          "kernel_ms_plain": kernel_ms_plain,
                          "achieved_plain": local_flops / (kernel_ms_plain * 1e-3) / 1e12,
                          "frac_plain": local_flops / (kernel_ms_plain * 1e-3) / 1e12 / peak_tf,
@@ -481,12 +776,23 @@ def run_ours(args, rank, world, local_rank):
                          "frac_of_sustained": achieved_sustained / sustained_peak_tf(),
                          "traffic": NCU_TRAFFIC_BYTES.get(args.workload)},
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(L)
+        if world > 1:
+            line["gather_check"] = gather_check
+            line["one_gpu_same_workload"] = one_gpu
+        if world == 1:
+            if not args.no_also:
+                line["library_baseline"] = library_baselines(sets, batch, L, nh_l)
+                line["also"] = other_configurations(bd)
+                if bd.device_status() != 0:
+                    raise RuntimeError("a kernel reported a device-side failure in the other configurations")
+            if not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline(L)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+        if rank == 0 and gather_check != "bit-exact":
+            raise SystemExit(f"gathered head outputs differ from the locally recomputed ones ({gather_check})")
 
 
 def run_sana(args):
@@ -498,61 +804,22 @@ def run_sana(args):
     import brodiffusion_b200 as bd
     torch.cuda.set_device(0)
     B, nh, N = SANA_WORKLOADS[args.workload]
-    Dm = nh * 32
-    byt = 4.0 * B * Dm * N * 2
-    n_sets = max(2, int(300e6 / byt) + 1)
-    gen = torch.Generator(device="cuda").manual_seed(4321)
-    sets = [tuple(torch.randn(B, Dm, N, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
-            for _ in range(n_sets)]
-    outs = [torch.empty(B, Dm, N, device="cuda", dtype=torch.bfloat16) for _ in range(n_sets)]
-
-    def step(i):
-        q, k, v = sets[i % n_sets]
-        bd.linear_attn_relu_fwd(q, k, v, outs[i % n_sets], nh, 32)
-
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(args.steps):
-                step(i)
-    torch.cuda.synchronize()
-    graph.replay()
-    torch.cuda.synchronize()
     sampler = ClockSampler(0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    e0.record()
-    graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    t_end = time.perf_counter() + 0.3
-    while time.perf_counter() < t_end:        # keep the GPU busy while the clock sampler collects
-        graph.replay()
-    torch.cuda.synchronize()
-    sampler.stop()
+    ms, gbs, n_sets, byt = measure_sana(bd, B, nh, N, steps=args.steps, sampler=sampler)
     if bd.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure")
     _, peak_gbs, kind = measured_peaks()
-    gbs = byt / (ms * 1e-3) / 1e9
     line = {"metric": "linear-attention GB/s", "value": gbs, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "batch": B, "heads": nh, "head_dim": 32, "tokens": N,
                        "l2": f"rotating {n_sets} input sets ({n_sets * byt / 1e6:.0f} MB > 126 MB L2)",
-                       "timing": "CUDA-graph replay of the steps"},
-            "clocks": sampler.summary(), "gpu_launches": args.steps,
+                       "timing": "CUDA-graph replay of the steps, median of 5"},
+            "clocks": sampler.summary(), "gpu_launches": args.steps * 5,
             "roofline": {"bound": "hbm", "kernel": "linear_attn_kernel", "achieved": gbs, "peak": peak_gbs,
                          "unit": "GB/s", "frac": gbs / peak_gbs, "peak_kind": f"{kind} copy bandwidth",
                          "traffic": None}}
     print(json.dumps(line), flush=True)
-
-
-PROJ_WORKLOADS = {"flux1024_qkv_proj": 3, "flux1024_out_proj": 1}
 
 
 def run_proj(args):
@@ -566,60 +833,19 @@ def run_proj(args):
     import brodiffusion_b200 as bd
     torch.cuda.set_device(0)
     n_proj = PROJ_WORKLOADS[args.workload]
-    L, Dm, nh, hd = 4608, 3072, 24, 128
-    gen = torch.Generator(device="cuda").manual_seed(9876)
-    n_sets = 6                                   # 6 x 28 MB of activations > 126 MB L2
-    xs = [torch.randn(L, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(n_sets)]
-    W = [torch.randn(Dm, Dm, device="cuda", dtype=torch.bfloat16, generator=gen) * 0.02 for _ in range(n_proj)]
-    outs = [torch.empty(L, Dm, device="cuda", dtype=torch.bfloat16) for _ in range(n_proj)]
-    gain = torch.ones(hd, device="cuda", dtype=torch.bfloat16)
-    cos, sin = bd.rope_tables_flux(512, 64, 64, hd)
-
-    def step(i):
-        x = xs[i % n_sets]
-        if n_proj == 3:
-            bd.qkv_norm_rope_fwd(x, W[0], W[1], W[2], outs[0], outs[1], outs[2], nh, hd, gain_q=gain, gain_k=gain,
-                                 cos=cos, sin=sin)
-        else:
-            bd.linear_fwd(x, W[0], None, outs[0])
-
-    for i in range(args.warmup):
-        step(i)
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    side = torch.cuda.Stream()
-    with torch.cuda.stream(side):
-        with torch.cuda.graph(graph, stream=side):
-            for i in range(args.steps):
-                step(i)
-    torch.cuda.synchronize()
-    graph.replay()
-    torch.cuda.synchronize()
     sampler = ClockSampler(0)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sampler.start()
-    e0.record()
-    graph.replay()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / args.steps
-    t_end = time.perf_counter() + 0.3
-    while time.perf_counter() < t_end:
-        graph.replay()
-    torch.cuda.synchronize()
-    sampler.stop()
+    ms, tf = measure_proj(bd, n_proj, steps=args.steps, sampler=sampler)
     if bd.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure")
     peak_tf, _, kind = measured_peaks()
-    tf = n_proj * 2.0 * L * Dm * Dm / (ms * 1e-3) / 1e12
     line = {"metric": "projection TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens": L, "in_features": Dm, "out_features": Dm,
-                       "projections": n_proj, "heads": nh, "head_dim": hd,
-                       "l2": f"rotating {n_sets} activation sets ({n_sets * L * Dm * 2 / 1e6:.0f} MB > 126 MB L2)",
-                       "timing": "CUDA-graph replay of the steps"},
-            "clocks": sampler.summary(), "gpu_launches": args.steps,
+            "config": {"workload": args.workload, "tokens": 4608, "in_features": 3072, "out_features": 3072,
+                       "projections": n_proj, "heads": 24, "head_dim": 128,
+                       "l2": "rotating 6 activation sets (170 MB > 126 MB L2)",
+                       "timing": "CUDA-graph replay of the steps, median of 5"},
+            "clocks": sampler.summary(), "gpu_launches": args.steps * 5,
             "roofline": {"bound": "tensor", "kernel": "gemm_wide_kernel", "achieved": tf, "peak": peak_tf,
                          "unit": "TFLOP/s", "frac": tf / peak_tf, "peak_kind": f"{kind} cuBLAS BF16 burst",
                          "traffic": None}}
@@ -655,16 +881,18 @@ def cpu_baseline(L):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--repeats", type=int, default=30,
+                    help="how many times the K-step timed region is measured (median reported)")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS) + sorted(SANA_WORKLOADS) + sorted(PROJ_WORKLOADS),
                     default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-also", action="store_true",
+                    help="skip the other configurations and the library baselines (1 GPU)")
     ap.add_argument("--q-norm", choices=["fused", "prepass"], default=None,
-                    help="RMSNorm + RoPE of Q inside the attention kernel or in the pre-pass "
-                         "(default prepass; fused is 1.5 % faster per step at 4608 tokens and 2.4 % "
-                         "slower at 16896, and its prologue counts against the kernel's roofline)")
+                    help="RMSNorm + RoPE of Q inside the attention kernel or in the pre-pass")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
     args = ap.parse_args()
@@ -674,6 +902,7 @@ def main():
     if args.workload is None:
         args.workload = "flux1024" if max(world, args.gpus) == 1 else "flux2048_headsharded"
     args.warmup = max(args.warmup, 3)
+    args.repeats = max(args.repeats, 1)
     if args.q_norm is None:
         args.q_norm = "prepass"
     if args.workload in SANA_WORKLOADS:
