@@ -1,11 +1,12 @@
 // Per-head RMSNorm followed by the rotary embedding, one pass over the tensor.
 //
 // Fast path (interleaved pairs, head_dim in {8, 16, 32, 64, 128, 256}, 16-byte
-// aligned rows): every lane owns 8 consecutive elements (one 16-byte vector,
-// four rotary pairs) of one (token, head) row, head_dim/8 neighbouring lanes
-// share a row and reduce its sum of squares by shuffles, and each warp keeps
-// four such vectors in flight so that enough bytes are outstanding to fill
-// HBM.  General path: one warp per (token, head) row, lane l handles rotary
+// aligned rows): a warp takes one token row and walks its heads; every lane owns
+// 8 consecutive elements (one 16-byte vector, four rotary pairs) of a head,
+// head_dim/8 neighbouring lanes share a head and reduce its sum of squares by
+// shuffles, the lane's slice of the row's cos / sin entries is loaded once and
+// reused for every head, and six vectors per lane are in flight so that enough
+// bytes are outstanding to fill HBM.  General path: one warp per (token, head) row, lane l handles rotary
 // pairs l, l+32, ...
 // The sum of squares is accumulated in FP32 (src/dit/qwenimage21.cpp:335-337)
 // and the result is rounded to the storage type once, after the rotation.
@@ -19,6 +20,11 @@ namespace bdattn {
 namespace {
 
 constexpr int kNormWarps = 8;
+
+// First CTA of each job in a launch that numbers its CTAs across the jobs.
+struct NormRopeGrid {
+    int block_begin[5];
+};
 
 template <bool kBf16>
 __device__ __forceinline__ float2 unpack2(uint32_t w) {
@@ -124,19 +130,27 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_rope_kernel(const NormRo
 
 
 // ---------------------------------------------------------------- fast path
+// One warp per token row, all heads of the row: the row's cos / sin slice is the
+// same for every head, so a lane loads it once and keeps it in registers while
+// the warp walks the heads (32 / kLpu heads at a time, kUnroll vectors per lane
+// in flight).  CTAs are numbered across the jobs of the launch (block_begin),
+// so a short job (the 512 text rows next to 4096 image rows) brings no idle CTAs.
 template <bool kBf16, int kLpu>   // kLpu = lanes per (token, head) row = head_dim / 8
-__global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a) {
-    constexpr int kUnroll = 4;
-    const NormRopeJobDev& job = a.job[blockIdx.y];
+__global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a, const NormRopeGrid g4) {
+    constexpr int kUnroll = 6;
+    constexpr int kHeadsPerStep = 32 / kLpu;
+    int j = 0;
+#pragma unroll
+    for (int i = 1; i < 4; ++i) j += (i < a.n_jobs && static_cast<int>(blockIdx.x) >= g4.block_begin[i]) ? 1 : 0;
+    const NormRopeJobDev& job = a.job[j];
     const int lane = threadIdx.x & 31;
     const int l = lane % kLpu;                 // this lane's 8-element slot inside the head
-    const int sub = lane / kLpu;               // which row of the warp's group
-    constexpr int kUnitsPerWarp = 32 / kLpu;
+    const int sub = lane / kLpu;               // which head of the step
     const int hd = kLpu * 8;
     const int half = hd / 2;
-    const long long n_units = static_cast<long long>(job.rows) * a.num_heads;
-    const long long warp_id = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    const long long n_warps = static_cast<long long>(gridDim.x) * (blockDim.x >> 5);
+    const int nh = a.num_heads;
+    const int warps = blockDim.x >> 5;
+    const int row_stride = (g4.block_begin[j + 1] - g4.block_begin[j]) * warps;
 
     float g[8];
 #pragma unroll
@@ -148,84 +162,79 @@ __global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a
                                    : load1<kBf16>(job.gain, l * 8 + i);
         }
     }
+    const float inv_hd = 1.0f / static_cast<float>(hd);
     const uint16_t* xin = reinterpret_cast<const uint16_t*>(job.x);
     uint16_t* xout = reinterpret_cast<uint16_t*>(job.out);
 
-    for (long long base = warp_id * kUnroll * kUnitsPerWarp; base < n_units;
-         base += n_warps * kUnroll * kUnitsPerWarp) {
-        uint4 v[kUnroll];
-        float4 cs[kUnroll], sn[kUnroll];
-        long long ooff[kUnroll];
-        bool live[kUnroll];
-#pragma unroll
-        for (int it = 0; it < kUnroll; ++it) {
-            const long long u = base + it * kUnitsPerWarp + sub;
-            live[it] = u < n_units;
-            // 32-bit division: a job has fewer than 2^31 (token, head) units (checked at launch)
-            const unsigned uu = live[it] ? static_cast<unsigned>(u) : 0u;
-            const int row = static_cast<int>(uu / static_cast<unsigned>(a.num_heads));
-            const int head = static_cast<int>(uu - static_cast<unsigned>(row) * static_cast<unsigned>(a.num_heads));
-            const long long xoff = static_cast<long long>(row) * job.x_ld + head * hd + l * 8;
-            ooff[it] = static_cast<long long>(row) * job.out_ld + head * hd + l * 8;
-            v[it] = live[it] ? *reinterpret_cast<const uint4*>(xin + xoff) : make_uint4(0, 0, 0, 0);
-            if (job.cos != nullptr) {
-                const long long t = static_cast<long long>(job.rope_row0 + row) * half + l * 4;
-                cs[it] = __ldg(reinterpret_cast<const float4*>(job.cos + t));
-                sn[it] = __ldg(reinterpret_cast<const float4*>(job.sin + t));
-            }
+    for (int row = (static_cast<int>(blockIdx.x) - g4.block_begin[j]) * warps + (threadIdx.x >> 5); row < job.rows;
+         row += row_stride) {
+        float c[4] = {1.0f, 1.0f, 1.0f, 1.0f}, sn[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (job.cos != nullptr) {
+            const long long t = static_cast<long long>(job.rope_row0 + row) * half + l * 4;
+            const float4 cv = __ldg(reinterpret_cast<const float4*>(job.cos + t));
+            const float4 sv = __ldg(reinterpret_cast<const float4*>(job.sin + t));
+            c[0] = cv.x; c[1] = cv.y; c[2] = cv.z; c[3] = cv.w;
+            sn[0] = sv.x; sn[1] = sv.y; sn[2] = sv.z; sn[3] = sv.w;
         }
+        const uint16_t* xrow = xin + static_cast<long long>(row) * job.x_ld + l * 8;
+        uint16_t* orow = xout + static_cast<long long>(row) * job.out_ld + l * 8;
+        for (int h0 = 0; h0 < nh; h0 += kHeadsPerStep * kUnroll) {
+            uint4 v[kUnroll];
 #pragma unroll
-        for (int it = 0; it < kUnroll; ++it) {
-            float2 p[4];
-            p[0] = unpack2<kBf16>(v[it].x);
-            p[1] = unpack2<kBf16>(v[it].y);
-            p[2] = unpack2<kBf16>(v[it].z);
-            p[3] = unpack2<kBf16>(v[it].w);
-            if (job.gain != nullptr) {
-                float ss = 0.0f;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) ss += p[i].x * p[i].x + p[i].y * p[i].y;
-#pragma unroll
-                for (int o = kLpu / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-                const float inv = rsqrtf(ss / static_cast<float>(hd) + a.eps);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    p[i].x = p[i].x * inv * g[2 * i];
-                    p[i].y = p[i].y * inv * g[2 * i + 1];
-                }
+            for (int it = 0; it < kUnroll; ++it) {
+                const int head = h0 + it * kHeadsPerStep + sub;
+                v[it] = head < nh ? *reinterpret_cast<const uint4*>(xrow + head * hd) : make_uint4(0, 0, 0, 0);
             }
-            if (job.cos != nullptr) {
-                const float c[4] = {cs[it].x, cs[it].y, cs[it].z, cs[it].w};
-                const float s[4] = {sn[it].x, sn[it].y, sn[it].z, sn[it].w};
+#pragma unroll
+            for (int it = 0; it < kUnroll; ++it) {
+                const int head = h0 + it * kHeadsPerStep + sub;
+                float2 p[4];
+                p[0] = unpack2<kBf16>(v[it].x);
+                p[1] = unpack2<kBf16>(v[it].y);
+                p[2] = unpack2<kBf16>(v[it].z);
+                p[3] = unpack2<kBf16>(v[it].w);
+                if (job.gain != nullptr) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ss += p[i].x * p[i].x + p[i].y * p[i].y;
+#pragma unroll
+                    for (int o = kLpu / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    const float inv = rsqrtf(ss * inv_hd + a.eps);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        p[i].x = p[i].x * inv * g[2 * i];
+                        p[i].y = p[i].y * inv * g[2 * i + 1];
+                    }
+                }
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float ra = p[i].x * c[i] - p[i].y * s[i];
-                    const float rb = p[i].x * s[i] + p[i].y * c[i];
+                    const float ra = p[i].x * c[i] - p[i].y * sn[i];
+                    const float rb = p[i].x * sn[i] + p[i].y * c[i];
                     p[i].x = ra;
                     p[i].y = rb;
                 }
-            }
-            if (live[it]) {
-                uint4 w;
-                w.x = pack2<kBf16>(p[0].x, p[0].y);
-                w.y = pack2<kBf16>(p[1].x, p[1].y);
-                w.z = pack2<kBf16>(p[2].x, p[2].y);
-                w.w = pack2<kBf16>(p[3].x, p[3].y);
-                *reinterpret_cast<uint4*>(xout + ooff[it]) = w;
+                if (head < nh) {
+                    uint4 w;
+                    w.x = pack2<kBf16>(p[0].x, p[0].y);
+                    w.y = pack2<kBf16>(p[1].x, p[1].y);
+                    w.z = pack2<kBf16>(p[2].x, p[2].y);
+                    w.w = pack2<kBf16>(p[3].x, p[3].y);
+                    *reinterpret_cast<uint4*>(orow + head * hd) = w;
+                }
             }
         }
     }
 }
 
 template <bool kBf16>
-cudaError_t launch_vec(const NormRopeArgs& a, int lpu, dim3 grid, cudaStream_t stream) {
+cudaError_t launch_vec(const NormRopeArgs& a, const NormRopeGrid& g4, int lpu, dim3 grid, cudaStream_t stream) {
     switch (lpu) {
-        case 1: norm_rope_vec_kernel<kBf16, 1><<<grid, 256, 0, stream>>>(a); break;
-        case 2: norm_rope_vec_kernel<kBf16, 2><<<grid, 256, 0, stream>>>(a); break;
-        case 4: norm_rope_vec_kernel<kBf16, 4><<<grid, 256, 0, stream>>>(a); break;
-        case 8: norm_rope_vec_kernel<kBf16, 8><<<grid, 256, 0, stream>>>(a); break;
-        case 16: norm_rope_vec_kernel<kBf16, 16><<<grid, 256, 0, stream>>>(a); break;
-        default: norm_rope_vec_kernel<kBf16, 32><<<grid, 256, 0, stream>>>(a); break;
+        case 1: norm_rope_vec_kernel<kBf16, 1><<<grid, 256, 0, stream>>>(a, g4); break;
+        case 2: norm_rope_vec_kernel<kBf16, 2><<<grid, 256, 0, stream>>>(a, g4); break;
+        case 4: norm_rope_vec_kernel<kBf16, 4><<<grid, 256, 0, stream>>>(a, g4); break;
+        case 8: norm_rope_vec_kernel<kBf16, 8><<<grid, 256, 0, stream>>>(a, g4); break;
+        case 16: norm_rope_vec_kernel<kBf16, 16><<<grid, 256, 0, stream>>>(a, g4); break;
+        default: norm_rope_vec_kernel<kBf16, 32><<<grid, 256, 0, stream>>>(a, g4); break;
     }
     return cudaGetLastError();
 }
@@ -254,13 +263,26 @@ cudaError_t launch_norm_rope(const NormRopeArgs& a, bool bf16, cudaStream_t stre
     }
     if (vec) {
         const int lpu = hd / 8;
-        const long long units_per_cta = 8LL * 4 * (32 / lpu);
-        long long blocks = (max_units + units_per_cta - 1) / units_per_cta;
-        const long long cap = 148LL * 8;
-        if (blocks > cap) blocks = cap;
-        if (blocks < 1) blocks = 1;
-        dim3 grid(static_cast<unsigned>(blocks), static_cast<unsigned>(a.n_jobs));
-        return bf16 ? launch_vec<true>(a, lpu, grid, stream) : launch_vec<false>(a, lpu, grid, stream);
+        // one warp per row; a long job is capped and its warps stride over the rows
+        long long total_rows = 0;
+        for (int i = 0; i < a.n_jobs; ++i) total_rows += a.job[i].rows;
+        const long long cap = static_cast<long long>(sm_count()) * 64;      // CTAs of the whole launch
+        NormRopeGrid g4 = {};
+        int begin = 0;
+        for (int i = 0; i < 4; ++i) {
+            g4.block_begin[i] = begin;
+            if (i < a.n_jobs) {
+                long long blocks = (a.job[i].rows + 7) / 8;
+                const long long share = (cap * a.job[i].rows + total_rows - 1) / total_rows;
+                if (blocks > share) blocks = share;
+                if (blocks < 1) blocks = 1;
+                begin += static_cast<int>(blocks);
+            }
+        }
+        g4.block_begin[4] = begin;
+        for (int i = a.n_jobs; i < 4; ++i) g4.block_begin[i + 1] = begin;
+        dim3 grid(static_cast<unsigned>(begin));
+        return bf16 ? launch_vec<true>(a, g4, lpu, grid, stream) : launch_vec<false>(a, g4, lpu, grid, stream);
     }
     long long blocks = (max_units + kNormWarps - 1) / kNormWarps;
     const long long cap = 148LL * 16;  // 16 resident 256-thread CTAs per SM
