@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(kNormWarps * 32) norm_rope_kernel(const NormRo
 // in flight).  CTAs are numbered across the jobs of the launch (block_begin),
 // so a short job (the 512 text rows next to 4096 image rows) brings no idle CTAs.
 template <bool kBf16, int kLpu>   // kLpu = lanes per (token, head) row = head_dim / 8
-__global__ void __launch_bounds__(256) norm_rope_vec_kernel(const NormRopeArgs a, const NormRopeGrid g4) {
+__global__ void __launch_bounds__(256, 4) norm_rope_vec_kernel(const NormRopeArgs a, const NormRopeGrid g4) {
     constexpr int kUnroll = 6;
     constexpr int kHeadsPerStep = 32 / kLpu;
     int j = 0;

@@ -6,8 +6,10 @@
 //   warps 4-7  : softmax of query tile 1
 //   warp  8    : issues every tcgen05.mma (one lane), owns the TMEM allocation
 //   warp  9    : TMA producer for Q, K and V tiles (one lane)
-//   warps 10-11: idle (they complete the third warpgroup so that registers
-//                can be moved to the softmax warpgroups with setmaxnreg)
+//   warps 10-11: with per-key scale vectors (kScale): multiply the rows of a K or
+//                V tile in shared memory by their factors before the MMAs read it;
+//                otherwise idle (they complete the third warpgroup so that
+//                registers can be moved to the softmax warpgroups with setmaxnreg)
 // Tensor memory (512 columns): S0 [0,128) S1 [128,256) O0 [256,256+HD)
 // O1 [256+HD,256+2HD).  P (the exponentiated scores, 16-bit, two per column)
 // is written back over the first 64 columns of its S tile and consumed from
@@ -123,9 +125,13 @@ __device__ __forceinline__ void setmaxnreg_dec() {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
-// HOOKS: 0 = none; 1 = key_mask only; 2 = key_mask, key_scale, val_scale, bias and the
-// per-row softmax statistics (slower softmax path).
-template <int HD, bool kBf16, int kHooks>
+// HOOKS: 0 = none; 1 = key_mask only; 2 = key_mask, bias and the per-row softmax
+// statistics (slower softmax path).
+// SCALE: key_scale / val_scale are applied to the K / V tiles in shared memory by
+// warp 10 (rounded to the storage type, as the reference's scale_inplace on its
+// k_full_ / v_full_ copies does, src/dit/qwenimage21_forward.cpp:606-645); the
+// softmax code does not change.
+template <int HD, bool kBf16, int kHooks, bool kScale>
 __global__ void __launch_bounds__(kThreads, 1)
 sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant__ CUtensorMap tmQ1,
                  const __grid_constant__ CUtensorMap tmK0, const __grid_constant__ CUtensorMap tmK1,
@@ -146,7 +152,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     uint64_t* p_full = s_full + 2;       // [2]
     uint64_t* pv_done = p_full + 2;      // [2]
     uint64_t* q_ready = pv_done + 2;     // [2]  Q tile normalised + rotated in place (fused Q path)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_ready + 2);
+    uint64_t* kv_ready = q_ready + 2;    // [ST] tile landed and, where needed, scaled (kScale)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_ready + ST);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -175,6 +182,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         for (int s = 0; s < ST; ++s) {
             mbar_init(&kv_full[s], 1);
             mbar_init(&kv_empty[s], 1);
+            mbar_init(&kv_ready[s], 2);           // warps 10 and 11
         }
         for (int t = 0; t < 2; ++t) {
             mbar_init(&s_full[t], 1);
@@ -362,29 +370,6 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             tmem_wait_ld();
 
             const TileInfo ti = kv_tile(a, j);
-            // Per-key vectors of the hooks are read by 16-byte loads on full,
-            // aligned tiles (the same addresses for every thread: broadcast loads);
-            // ragged or unaligned tiles take the element-wise path.
-            auto hook_vec = [&](const float* p) {
-                return ti.valid == kBN && ((reinterpret_cast<uintptr_t>(p + ti.kbase) & 15u) == 0);
-            };
-            if constexpr (kHooks == 2) {
-                if (a.key_scale != nullptr) {
-                    if (hook_vec(a.key_scale)) {
-                        const float4* kv4 = reinterpret_cast<const float4*>(a.key_scale + ti.kbase);
-#pragma unroll
-                        for (int c4 = 0; c4 < kBN / 4; ++c4) {
-                            const float4 f = __ldg(kv4 + c4);
-                            s[4 * c4] *= f.x; s[4 * c4 + 1] *= f.y; s[4 * c4 + 2] *= f.z; s[4 * c4 + 3] *= f.w;
-                        }
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < kBN; ++c) {
-                            if (c < ti.valid) s[c] *= __ldg(a.key_scale + ti.kbase + c);
-                        }
-                    }
-                }
-            }
             if constexpr (kHooks == 2) {
                 if (a.bias != nullptr) {
                     const int br = q_glob - a.bias_row0;
@@ -460,23 +445,6 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
 #pragma unroll
             for (int ch = 0; ch < 4; ++ch) {
                 uint32_t pk[16];
-                float vsc[32];
-                if constexpr (kHooks == 2) {
-                    if (a.val_scale != nullptr) {
-                        if (hook_vec(a.val_scale)) {
-                            const float4* vs4 = reinterpret_cast<const float4*>(a.val_scale + ti.kbase + ch * 32);
-#pragma unroll
-                            for (int c4 = 0; c4 < 8; ++c4) {
-                                const float4 f = __ldg(vs4 + c4);
-                                vsc[4 * c4] = f.x; vsc[4 * c4 + 1] = f.y; vsc[4 * c4 + 2] = f.z; vsc[4 * c4 + 3] = f.w;
-                            }
-                        } else {
-#pragma unroll
-                            for (int c = 0; c < 32; ++c)
-                                vsc[c] = (ch * 32 + c < ti.valid) ? __ldg(a.val_scale + ti.kbase + ch * 32 + c) : 1.0f;
-                        }
-                    }
-                }
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const int c0 = ch * 32 + 2 * i;
@@ -485,12 +453,6 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     p0 = fast_exp2(x0);
                     p1 = fast_exp2(x1);
                     fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
-                    if constexpr (kHooks == 2) {
-                        if (a.val_scale != nullptr) {
-                            p0 *= vsc[2 * i];
-                            p1 *= vsc[2 * i + 1];
-                        }
-                    }
                     pk[i] = pack2<kBf16>(p0, p1);
                 }
                 tmem_st16(tS + ch * 16, pk);
@@ -585,6 +547,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             constexpr uint32_t idesc_pv = make_idesc_f16(kFmt, kBM, HD, 0, 1);
             const uint32_t q_base = smem_u32(smem_q);
             const uint32_t kv_base = smem_u32(smem_kv);
+            uint64_t* const kv_rdy = kScale ? kv_ready : kv_full;
 
             auto issue_qk = [&](int t, int slot) {
                 const uint32_t qa = q_base + t * C::kQBytes;
@@ -609,7 +572,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
             bool ok = n_kv > 0;
             if (ok) ok = mbar_wait(&q_full[0], 0) && mbar_wait(&q_full[1], 0);
             if (ok && a.q_fused) ok = mbar_wait(&q_ready[0], 0) && mbar_wait(&q_ready[1], 0);
-            if (ok) ok = mbar_wait(&kv_full[0], 0);
+            if (ok) ok = mbar_wait(&kv_rdy[0], 0);
             if (ok) {
                 tc_fence_after();
                 if (lane == 0) {
@@ -628,8 +591,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 int kslot = vslot + 1, kphase = vphase;
                 if (kslot == ST) { kslot = 0; kphase ^= 1; }
                 const bool more = j + 1 < n_kv;
-                ok = mbar_wait(&kv_full[vslot], static_cast<uint32_t>(vphase));
-                if (ok && more) ok = mbar_wait(&kv_full[kslot], static_cast<uint32_t>(kphase));
+                ok = mbar_wait(&kv_rdy[vslot], static_cast<uint32_t>(vphase));
+                if (ok && more) ok = mbar_wait(&kv_rdy[kslot], static_cast<uint32_t>(kphase));
                 if (ok) ok = mbar_wait(&p_full[0], static_cast<uint32_t>(j & 1));
                 if (!ok) break;
                 tc_fence_after();
@@ -700,6 +663,92 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                 }
             }
             __syncwarp();
+        } else if (warp >= 10) {
+            // ------------------------------------------- K / V row scaling
+            // Warps 10 and 11 both walk the ring items in order (each sees every phase
+            // of the barriers it waits on) and take half of a tile's lines each.  The
+            // row factors of an item are fetched before the wait for its tile.  A tile
+            // none of whose factors differs from one is passed on as it is; otherwise
+            // every 128-byte line (one row of a 64-column chunk; the swizzle permutes
+            // inside the line only) is multiplied by its row's factor.
+            if constexpr (kScale) {
+                const int half_id = warp - 10;
+                bool ok = true;
+                // row factors of item i (rows lane, lane + 32, ...), fetched one item ahead
+                auto fetch = [&](int i, float (&f)[4]) {
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) f[w] = 1.0f;
+                    const float* sc = (i & 1) ? a.val_scale : a.key_scale;
+                    if (sc != nullptr && i < 2 * n_kv) {
+                        const TileInfo ti = kv_tile(a, i >> 1);
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const int r = lane + 32 * w;
+                            if (r < ti.valid) f[w] = __ldg(sc + ti.kbase + r);
+                        }
+                    }
+                };
+                float f[4], fn[4];
+                fetch(0, fn);
+                for (int i = 0; ok && i < 2 * n_kv; ++i) {
+                    const int slot = i % ST;
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) f[w] = fn[w];
+                    fetch(i + 1, fn);
+                    const bool ne = f[0] != 1.0f || f[1] != 1.0f || f[2] != 1.0f || f[3] != 1.0f;
+                    const bool scale_tile = __any_sync(0xffffffffu, ne);
+                    ok = mbar_wait(&kv_full[slot], static_cast<uint32_t>((i / ST) & 1));
+                    if (!ok) break;
+                    if (scale_tile) {
+                        uint8_t* tile = smem_kv + slot * C::kTileBytes;
+                        // lane -> 16-byte piece (lane & 7) of row 4 * g + (lane >> 3) of a chunk;
+                        // this warp takes the row groups g of its parity
+                        constexpr int kIters = 16 * C::kChunks;
+                        constexpr int kBatch = 4;       // loads of a batch are issued before its stores
+#pragma unroll 1
+                        for (int it0 = 0; it0 < kIters; it0 += kBatch) {
+                            uint4 v[kBatch];
+                            float fr[kBatch];
+#pragma unroll
+                            for (int b = 0; b < kBatch; ++b) {
+                                const int it = it0 + b;
+                                const int g = ((it & 15) << 1) + half_id;      // row group 0..31
+                                const int r = (g << 2) + (lane >> 3);
+                                const int fw = g >> 3;                          // = r >> 5, the same for the whole warp
+                                const float fsel = fw == 0 ? f[0] : (fw == 1 ? f[1] : (fw == 2 ? f[2] : f[3]));
+                                fr[b] = __shfl_sync(0xffffffffu, fsel, r & 31);
+                                v[b] = *reinterpret_cast<const uint4*>(tile + (it >> 4) * kChunkBytes + r * 128 + ((lane & 7) << 4));
+                            }
+#pragma unroll
+                            for (int b = 0; b < kBatch; ++b) {
+                                uint32_t* w32 = reinterpret_cast<uint32_t*>(&v[b]);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    float lo, hi;
+                                    if constexpr (kBf16) {
+                                        lo = __uint_as_float(w32[e] << 16);
+                                        hi = __uint_as_float(w32[e] & 0xffff0000u);
+                                    } else {
+                                        const __half2 h = *reinterpret_cast<const __half2*>(&w32[e]);
+                                        lo = __low2float(h);
+                                        hi = __high2float(h);
+                                    }
+                                    w32[e] = pack2<kBf16>(lo * fr[b], hi * fr[b]);
+                                }
+                            }
+#pragma unroll
+                            for (int b = 0; b < kBatch; ++b) {
+                                const int it = it0 + b;
+                                const int r = ((((it & 15) << 1) + half_id) << 2) + (lane >> 3);
+                                *reinterpret_cast<uint4*>(tile + (it >> 4) * kChunkBytes + r * 128 + ((lane & 7) << 4)) = v[b];
+                            }
+                        }
+                        fence_proxy_async_smem();      // the MMA reads the tile through the async proxy
+                    }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&kv_ready[slot]);
+                }
+            }
         }
     }
 
@@ -711,10 +760,10 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     }
 }
 
-template <int HD, bool kBf16, int kHooks>
+template <int HD, bool kBf16, int kHooks, bool kScale>
 cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     using C = Cfg<HD>;
-    auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks>;
+    auto kern = sdpa_tc05_kernel<HD, kBf16, kHooks, kScale>;
     cudaError_t e = set_max_smem_once(kern, C::kSmemBytes);
     if (e != cudaSuccess) return e;
     dim3 grid(static_cast<unsigned>(L.q_ctas), static_cast<unsigned>(L.num_heads),
@@ -726,13 +775,18 @@ cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
 
 template <int HD, bool kBf16>
 cudaError_t launch_hd(const SdpaLaunch& L, cudaStream_t stream) {
-    // 2: every hook; 1: key mask only (the common case: padded captions), kept free of
-    // the other hooks' code; 0: none
-    const bool all_hooks = L.args.key_scale != nullptr || L.args.val_scale != nullptr ||
-                           L.args.bias != nullptr || L.args.lse != nullptr;
-    if (all_hooks) return launch_t<HD, kBf16, 2>(L, stream);
-    if (L.args.key_mask != nullptr) return launch_t<HD, kBf16, 1>(L, stream);
-    return launch_t<HD, kBf16, 0>(L, stream);
+    // 2: every softmax hook; 1: key mask only (the common case: padded captions), kept
+    // free of the other hooks' code; 0: none.  The per-key scale vectors are handled
+    // outside the softmax (kScale) and combine with 0 or 2.
+    const bool all_hooks = L.args.bias != nullptr || L.args.lse != nullptr;
+    const bool scale = L.args.key_scale != nullptr || L.args.val_scale != nullptr;
+    if (scale) {
+        if (all_hooks || L.args.key_mask != nullptr) return launch_t<HD, kBf16, 2, true>(L, stream);
+        return launch_t<HD, kBf16, 0, true>(L, stream);
+    }
+    if (all_hooks) return launch_t<HD, kBf16, 2, false>(L, stream);
+    if (L.args.key_mask != nullptr) return launch_t<HD, kBf16, 1, false>(L, stream);
+    return launch_t<HD, kBf16, 0, false>(L, stream);
 }
 
 }  // namespace

@@ -86,7 +86,11 @@ int bdattn_device_status(int* status, int clear);
  *
  * key_scale / val_scale (optional, Lk floats each over the concatenated keys)
  * multiply K rows and V rows on the fly: the prefix K/V attenuation hook of
- * src/dit/qwenimage21_forward.cpp:606-645 without touching the cache.
+ * src/dit/qwenimage21_forward.cpp:606-645 without touching the cache.  The
+ * tensor-core kernel scales the rows of the tiles it has staged in shared
+ * memory and rounds them to the tensor dtype, which is what the reference's
+ * scale_inplace on its k_full_ / v_full_ copies does; tiles whose factors are
+ * all one are passed through untouched.
  *
  * head_dim 64 and 128 run on the tcgen05 tensor-core kernel; other head
  * dims (multiple of 8, <= 256) run on a general kernel.  dtype BF16 or F16.

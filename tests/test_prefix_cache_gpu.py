@@ -62,3 +62,23 @@ def test_cached_step_with_scaled_cache_equals_scale_hooks(bd, oracle):
     vs = oracle.prefix_cache_scale(vc, 0.5, synth.round_bf16)
     ref = oracle.sdpa(q, np.concatenate([ks, kf]), np.concatenate([vs, vf]), nh)
     G.check(G.host(out), ref, what="cached step over a scaled prefix cache")
+    # the hooks on the un-scaled cache: the kernel scales the prefix rows of its K / V
+    # tiles in shared memory and rounds them to BF16 like scale_inplace does, so the
+    # two ways agree bit for bit
+    ksv, vsv = np.ones(P + T, np.float32), np.ones(P + T, np.float32)
+    ksv[:P], vsv[:P] = 1.5, 0.5
+    out_h = torch.empty_like(out)
+    bd.sdpa_fwd(G.dev(q), [G.dev(kc), G.dev(kf)], [G.dev(vc), G.dev(vf)], out_h, nh,
+                key_scale=G.dev(ksv, torch.float32), val_scale=G.dev(vsv, torch.float32))
+    assert bd.device_status() == 0
+    assert torch.equal(out_h, out)
+    # and with a key mask on top (the scale and mask hooks together)
+    km = np.ones(P + T, np.float32)
+    km[P + 100:P + 130] = 0.0
+    out_m = torch.empty_like(out)
+    bd.sdpa_fwd(G.dev(q), [G.dev(kc), G.dev(kf)], [G.dev(vc), G.dev(vf)], out_m, nh,
+                key_scale=G.dev(ksv, torch.float32), val_scale=G.dev(vsv, torch.float32),
+                key_mask=G.dev(km, torch.float32))
+    assert bd.device_status() == 0
+    ref_m = oracle.sdpa(q, np.concatenate([ks, kf]), np.concatenate([vs, vf]), nh, key_mask=km)
+    G.check(G.host(out_m), ref_m, what="scaled prefix cache with a key mask")
