@@ -71,18 +71,19 @@ EncodeTiledFn encode_tiled_fn() {
 // 128-byte swizzle, zero fill outside the tensor.
 int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, long long cols,
                 long long rows, long long batch, long long ld, long long batch_stride,
-                int box_rows) {
+                int box_rows, int box_cols = 64, bool swizzle = true) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail("%s: cuTensorMapEncodeTiled is not available from the driver", op);
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
                           static_cast<cuuint64_t>(batch)};
     if (batch_stride <= 0) batch_stride = rows * ld;
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(ld) * 2, static_cast<cuuint64_t>(batch_stride) * 2};
-    cuuint32_t box[3] = {64, static_cast<cuuint32_t>(box_rows), 1};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         return fail("%s: cuTensorMapEncodeTiled failed (CUresult %d) for base=%p cols=%lld rows=%lld "
@@ -628,7 +629,8 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     a.eps = eps; a.sz_in = sz_in; a.w_in = w_in; a.sz_out = sz_out;
     const long long D = static_cast<long long>(num_heads) * 32;
     CUtensorMap tq, tk, tv, to;
-    if (make_map_3d(op, &to, out, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
+    // output: one 16-token x 32-row piece per warp and store, plain row-major in shared memory
+    if (make_map_3d(op, &to, out, true, n_tokens, D, batch, ld, a.batch_stride, 32, 16, false)) return -1;
     if (make_map_3d(op, &tq, q, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tk, k, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tv, v, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;

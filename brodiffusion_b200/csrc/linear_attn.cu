@@ -37,6 +37,7 @@ constexpr int kLaChunk = 128;                 // tokens per ring item
 constexpr int kLaMaxStages = 8;               // ring of 16 KB items: 8 with one CTA per SM, 3 when two share it
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
+constexpr int kLaPieceBytes = 32 * 16 * 2;    // output piece of one warp and chunk: 32 rows x 16 tokens, row-major
 constexpr int kLaState = 33 * 32;             // [S; z] floats
 constexpr int kLaStLd = 40;                   // row stride of the state tile in shared memory: the fragment
                                               // loads of the apply pass (rows over g, columns over q4) then
@@ -46,7 +47,7 @@ struct LaSmem {
     float partial[kLaWarps][kLaState];
     float local_state[kLaState];
     float state[48 * kLaStLd];   // rows 33..47 zero
-    alignas(1024) uint8_t out_stage[2][2 * kLaBoxBytes];   // two 32 x 128-token output tiles, box layout
+    alignas(1024) uint8_t out_stage[kLaWarps][2][kLaPieceBytes];   // per warp: two 32-row x 16-token output pieces
     uint64_t full[kLaMaxStages];
     uint64_t empty[kLaMaxStages];
     alignas(1024) uint8_t ring[1][kLaSlotBytes];   // a.stages items follow (dynamic shared memory)
@@ -332,7 +333,14 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int sub = 0; sub < 2; ++sub) {
             const int cidx = 2 * (it - n_mine) + sub;     // 128-token chunk of this CTA
             if (cidx >= n_mine) break;
-            uint8_t* stage = sm.out_stage[cidx & 1];
+            // Every warp stages and stores its own 32-row x 16-token piece (TMA store
+            // issued by its lane 0), so no barrier of the CTA sits between chunks and
+            // the warps drift apart, which hides the latency chain of a chunk (tile
+            // load, MMAs, reciprocal, packing).  Two pieces per warp alternate: before
+            // a piece is overwritten, the store that last read it has finished reading.
+            uint8_t* stage = sm.out_stage[warp][cidx & 1];
+            if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+            __syncwarp();
             if (ok) {
                 const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (2 * sub + box) * kLaBoxBytes;
 #pragma unroll
@@ -357,37 +365,29 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
                     const float r0 = 1.0f / (den0 + a.eps);
                     const float r1 = 1.0f / (den1 + a.eps);
-                    // the tile is staged in the layout of two 64-token TMA boxes
-                    // (128-byte swizzle), which also keeps these writes conflict-free
-                    const int tok = (warp & 3) * 16 + nt * 8 + q4 * 2;      // inside the 64-token box
-                    uint8_t* sbox = stage + box * kLaBoxBytes + (tok & 7) * 2;
+                    // row-major piece, 32 bytes per row: lanes g = 0..7 of a store fall
+                    // into eight different 32-byte rows, q4 into its words: no conflicts
+                    uint8_t* sp = stage + (nt * 8 + q4 * 2) * 2;
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
                         const int i0 = mt * 16 + g;
-                        *reinterpret_cast<uint32_t*>(sbox + swz(i0, tok >> 3)) = pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
-                        *reinterpret_cast<uint32_t*>(sbox + swz(i0 + 8, tok >> 3)) = pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
+                        *reinterpret_cast<uint32_t*>(sp + i0 * 32) = pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
+                        *reinterpret_cast<uint32_t*>(sp + (i0 + 8) * 32) = pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
                     }
                 }
             }
-            // The staged tile leaves by TMA (one thread, asynchronous), so the warps go
-            // straight on to the next chunk.  Before the barrier the issuing thread
-            // makes sure its earlier stores have finished reading shared memory: the
-            // buffer the next chunk is staged in was last read by the store of the
-            // chunk before this one.
             fence_proxy_async_smem();
-            if (tid == 0) tma_store_wait_read_all();
-            asm volatile("bar.sync 1, 256;" ::: "memory");   // the 32 x 128 output tile is complete
-            if (ok && tid == 0) {
-                const int tok0 = (c_begin + cidx) * kLaChunk;
-                tma_store_3d(&tmO, stage, tok0, row0, batch);
-                if (tok0 + 64 < a.n_tokens) tma_store_3d(&tmO, stage + kLaBoxBytes, tok0 + 64, row0, batch);
+            __syncwarp();
+            if (ok && lane == 0) {
+                const int tok = (c_begin + cidx) * kLaChunk + box * 64 + (warp & 3) * 16;
+                if (tok < a.n_tokens) tma_store_3d(&tmO, stage, tok, row0, batch);
                 tma_store_commit();
             }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.empty[slot]);
     }
-    if (tid == 0) tma_store_wait_all();     // shared memory stays valid until the last store has left
+    if (lane == 0) tma_store_wait_all();    // shared memory stays valid until the last store has left
     phase_sync();
 }
 
