@@ -24,6 +24,7 @@ __all__ = [
 
 F32, F16, BF16 = 0, 1, 2
 MASK_NONE, MASK_CAUSAL = 0, 1
+STATUS_WAIT_TIMEOUT, STATUS_BAD_ARGS = 1, 2
 ROPE_INTERLEAVED, ROPE_HALF_SPLIT = 0, 1
 
 
@@ -131,6 +132,13 @@ def lib():
         L.bdattn_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
         L.bdattn_sdpa_fwd_allgather.argtypes = [C.POINTER(SdpaParams), C.POINTER(C.c_void_p),
                                                 C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+        L.bdattn_mgpu_init.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int]
+        L.bdattn_mgpu_destroy.argtypes = [C.c_void_p]
+        L.bdattn_mgpu_size.argtypes = [C.c_void_p]
+        L.bdattn_mgpu_barrier.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+        L.bdattn_mgpu_sdpa_fwd_headsharded.argtypes = [C.c_void_p, C.c_int, C.POINTER(SdpaParams),
+                                                       C.POINTER(C.c_void_p), C.c_longlong, C.c_longlong,
+                                                       C.c_int, C.c_void_p]
         L.bdattn_sdpa_traced_workspace_bytes.restype = C.c_size_t
         L.bdattn_sdpa_traced_workspace_bytes.argtypes = [C.c_int, C.c_int]
         L.bdattn_sdpa_traced_fwd.argtypes = [C.POINTER(SdpaParams), C.POINTER(TraceParams), C.c_void_p]
@@ -219,7 +227,7 @@ def device_status(clear: bool = True) -> int:
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
              val_scale=None, softmax_scale=0.0, num_kv_heads=0, q_norm=None, stream=None,
-             peer_out_ptrs=None, _trace=None):
+             peer_out_ptrs=None, _trace=None, _mgpu=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
     (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
@@ -275,6 +283,12 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
     if _trace is not None:
         _check(lib().bdattn_sdpa_traced_fwd(C.byref(p), C.byref(_trace), _stream(stream)))
         return
+    if _mgpu is not None:
+        ctx, rank, replica_ptrs, replica_ld, replica_bs, total_heads = _mgpu
+        arr = (C.c_void_p * len(replica_ptrs))(*replica_ptrs)
+        _check(lib().bdattn_mgpu_sdpa_fwd_headsharded(ctx, rank, C.byref(p), arr, replica_ld, replica_bs,
+                                                      total_heads, _stream(stream)))
+        return
     if peer_out_ptrs:
         n = len(peer_out_ptrs[0])
         a0 = (C.c_void_p * max(n, 1))(*peer_out_ptrs[0])
@@ -282,6 +296,40 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
         _check(lib().bdattn_sdpa_fwd_allgather(C.byref(p), a0, a1, n, _stream(stream)))
         return
     _check(lib().bdattn_sdpa_fwd(C.byref(p), _stream(stream)))
+
+
+class MultiGpu:
+    """``bdattn_mgpu_*``: several GPUs driven from one process, one host thread per
+    GPU.  ``replicas`` are the callers' full-output tensors, one per GPU."""
+
+    def __init__(self, devices):
+        self.devices = list(devices)
+        h = C.c_void_p()
+        arr = (C.c_int * len(self.devices))(*self.devices)
+        _check(lib().bdattn_mgpu_init(C.byref(h), arr, len(self.devices)))
+        self.handle = h
+
+    def size(self) -> int:
+        return int(lib().bdattn_mgpu_size(self.handle))
+
+    def sdpa_fwd_headsharded(self, rank, q, k, v, replicas, total_heads, **kw):
+        """q, k, v: this rank's head columns (tensor or segment lists as for
+        ``sdpa_fwd``); replicas: list of (B, L, D) or (L, D) tensors, one per GPU."""
+        r0 = replicas[0]
+        ld = r0.stride(-2)
+        bs = r0.stride(0) if r0.dim() == 3 else 0
+        qs = list(q) if isinstance(q, (list, tuple)) else [q]
+        dummy = [t for t in qs]          # shapes only: the library derives the output pointers
+        sdpa_fwd(q, k, v, dummy if isinstance(q, (list, tuple)) else dummy[0], total_heads // len(replicas),
+                 _mgpu=(self.handle, rank, [t.data_ptr() for t in replicas], ld, bs, total_heads), **kw)
+
+    def barrier(self, rank, timeout_ms=0, stream=None):
+        _check(lib().bdattn_mgpu_barrier(self.handle, rank, timeout_ms, _stream(stream)))
+
+    def destroy(self):
+        if self.handle is not None:
+            lib().bdattn_mgpu_destroy(self.handle)
+            self.handle = None
 
 
 def rmsnorm_rope(jobs, num_heads, head_dim, *, eps=1e-6, pair_mode=ROPE_INTERLEAVED, stream=None):

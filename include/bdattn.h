@@ -166,6 +166,58 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream);
 
+/* ------------------------------------------------ several GPUs, one process
+ * Set-up and completion for a caller that drives the GPUs of one node from one
+ * process with one host thread per GPU (no counterpart in the reference, which
+ * is single-device; conventions as above, after
+ * include/brodiffusion/qwenimage21_capi.h:32-37: opaque handle, 0 / -1 returns,
+ * bdattn_last_error()).
+ *
+ *   bdattn_mgpu_init     enables peer access between the listed devices (at most
+ *                        BDATTN_MGPU_MAX, all different) and allocates, on each, a
+ *                        small array of arrival counters.  This is the one call of
+ *                        the library that allocates device memory; _destroy frees
+ *                        it.  Call it once, from any thread, before the workers.
+ *   bdattn_mgpu_sdpa_fwd_headsharded
+ *                        rank r (its device current) computes ITS heads of the
+ *                        attention p describes (p->num_heads = total_heads / n,
+ *                        q/k/v pointing at that rank's head columns; p->o is
+ *                        ignored) and stores them into the head columns
+ *                        [r * num_heads * head_dim, ...) of EVERY replica:
+ *                        replicas[g] is GPU g's caller-owned copy of the full
+ *                        (batch, L, total_heads * head_dim) output, row stride
+ *                        replica_ld, batch stride replica_batch_stride (elements).
+ *                        This is bdattn_sdpa_fwd_allgather with the peer pointers
+ *                        worked out by the library.
+ *   bdattn_mgpu_barrier  enqueues, on rank r's stream, a kernel that tells every
+ *                        peer that r has arrived and waits until every peer has
+ *                        arrived too.  Once it has passed on a rank's stream, all
+ *                        ranks' work enqueued before their own barrier call is
+ *                        complete, so the local replica holds all heads.  The wait
+ *                        is bounded: after timeout_ms (0 = 2000) the kernel sets
+ *                        BDATTN_STATUS_WAIT_TIMEOUT in that GPU's status word and
+ *                        returns normally; bdattn_device_status reports it and the
+ *                        context stays usable.  Every rank must enqueue the same
+ *                        number of barriers; a rank that skipped one catches up by
+ *                        calling it, or the context is re-created.
+ * Plain peer stores and local loads only: no TMA multicast, no multimem, no NVLS.
+ */
+#define BDATTN_MGPU_MAX 8
+typedef struct bdattn_mgpu bdattn_mgpu;
+
+int bdattn_mgpu_init(bdattn_mgpu** ctx, const int* devices, int n_gpus);
+
+int bdattn_mgpu_destroy(bdattn_mgpu* ctx);
+
+int bdattn_mgpu_size(const bdattn_mgpu* ctx);
+
+int bdattn_mgpu_sdpa_fwd_headsharded(bdattn_mgpu* ctx, int rank, const bdattn_sdpa_params* p,
+                                     void* const* replicas, long long replica_ld,
+                                     long long replica_batch_stride, int total_heads,
+                                     bdattn_stream_t stream);
+
+int bdattn_mgpu_barrier(bdattn_mgpu* ctx, int rank, int timeout_ms, bdattn_stream_t stream);
+
 /* Traced / steered attention on the device.
  *
  * Replaces the host round trip of dit::joint_attention_traced
