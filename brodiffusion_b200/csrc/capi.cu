@@ -3,6 +3,7 @@
 // stream the caller passes.
 #include "../../include/bdattn.h"
 
+#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -140,6 +141,10 @@ int make_map_2d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
                     op, static_cast<int>(r), base, cols, rows, ld);
     return 0;
 }
+
+// 1: head-sharded calls (n_peers > 0) run on the persistent kernel with the peer push;
+// 0: on the one-item-per-CTA kernel whose epilogue stores to the peers itself.
+std::atomic<int> g_allgather_mode{1};
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -376,7 +381,10 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         L.head_dim = hd_kernel;
         L.bf16 = bf16;
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
-        cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
+        // the head-sharded call runs on the persistent kernel, whose spare warps push
+        // finished tiles to the peers behind the computation (bdattn_sdpa_allgather_mode)
+        cudaError_t e = (n_peers > 0 && g_allgather_mode.load() == 1) ? bdattn::launch_sdpa_tc05_persistent(L, st)
+                                                                      : bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
         return 0;
     }
@@ -417,6 +425,11 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream) {
     return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, nullptr, stream);
+}
+
+int bdattn_sdpa_allgather_mode(int mode) {
+    if (mode != 0 && mode != 1) return g_allgather_mode.load();
+    return g_allgather_mode.exchange(mode);
 }
 
 size_t bdattn_sdpa_traced_workspace_bytes(int num_heads, int q_rows_total) {
