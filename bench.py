@@ -543,7 +543,8 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         return "bit-exact" if int(flag.item()) == 1 else "mismatch"
 
-    bd.sdpa_allgather_mode(0 if args.gather_kernel == "epilogue" else 1)
+    bd.sdpa_allgather_mode({"epilogue": 0, "persistent": 1, "auto": 2}[args.gather_kernel])
+    uses_persistent = args.gather_kernel == "persistent" or (args.gather_kernel == "auto" and world - 1 >= 3)
     for i in range(args.warmup):
         step(i)
     barrier()
@@ -553,7 +554,7 @@ def run_ours(args, rank, world, local_rank):
     # checked once before anything is timed and the run falls back to the kernel whose
     # epilogue stores to the peers itself if its gathered heads are not bit-exact.
     gather_kernel = None
-    if world > 1 and gathered is not None and args.gather_kernel == "epilogue":
+    if world > 1 and gathered is not None and not uses_persistent:
         gather_kernel = "epilogue peer stores"
     elif world > 1 and gathered is not None:
         gather_kernel = "persistent kernel, peer push by spare warps"
@@ -919,9 +920,10 @@ def main():
                     help="RMSNorm + RoPE of Q inside the attention kernel or in the pre-pass")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
-    ap.add_argument("--gather-kernel", choices=["persistent", "epilogue"], default="persistent",
+    ap.add_argument("--gather-kernel", choices=["auto", "persistent", "epilogue"], default="auto",
                     help="N > 1, fused gather: persistent kernel whose spare warps push finished tiles to the "
-                         "peers, or the one-item-per-CTA kernel whose epilogue stores to the peers")
+                         "peers, the one-item-per-CTA kernel whose epilogue stores to the peers, or the "
+                         "library's choice by the number of peers (persistent from three peers on)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

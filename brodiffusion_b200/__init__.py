@@ -333,9 +333,10 @@ class MultiGpu:
 
 
 def sdpa_allgather_mode(mode: int = -1) -> int:
-    """``bdattn_sdpa_allgather_mode``: 1 = persistent kernel with the peer push
-    (default), 0 = epilogue stores by the one-item-per-CTA kernel; returns the
-    previous mode, any other argument only queries."""
+    """``bdattn_sdpa_allgather_mode``: 1 = persistent kernel with the peer push,
+    0 = epilogue stores by the one-item-per-CTA kernel, 2 = by the number of peers
+    (default: persistent from three peers on); returns the previous mode, any other
+    argument only queries."""
     return int(lib().bdattn_sdpa_allgather_mode(mode))
 
 

@@ -142,9 +142,11 @@ int make_map_2d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
     return 0;
 }
 
-// 1: head-sharded calls (n_peers > 0) run on the persistent kernel with the peer push;
-// 0: on the one-item-per-CTA kernel whose epilogue stores to the peers itself.
-std::atomic<int> g_allgather_mode{1};
+// Kernel of the head-sharded calls (n_peers > 0): 1 = the persistent kernel with the
+// peer push, 0 = the one-item-per-CTA kernel whose epilogue stores to the peers itself,
+// 2 = by the number of peers (persistent from three peers on).
+std::atomic<int> g_allgather_mode{2};
+constexpr int kPersistentFromPeers = 3;
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -383,8 +385,9 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
         // the head-sharded call runs on the persistent kernel, whose spare warps push
         // finished tiles to the peers behind the computation (bdattn_sdpa_allgather_mode)
-        cudaError_t e = (n_peers > 0 && g_allgather_mode.load() == 1) ? bdattn::launch_sdpa_tc05_persistent(L, st)
-                                                                      : bdattn::launch_sdpa_tc05(L, st);
+        const int gmode = g_allgather_mode.load();
+        const bool persistent = n_peers > 0 && (gmode == 1 || (gmode == 2 && n_peers >= kPersistentFromPeers));
+        cudaError_t e = persistent ? bdattn::launch_sdpa_tc05_persistent(L, st) : bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
         return 0;
     }
@@ -428,7 +431,7 @@ int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0,
 }
 
 int bdattn_sdpa_allgather_mode(int mode) {
-    if (mode != 0 && mode != 1) return g_allgather_mode.load();
+    if (mode < 0 || mode > 2) return g_allgather_mode.load();
     return g_allgather_mode.exchange(mode);
 }
 
