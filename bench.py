@@ -543,29 +543,11 @@ def run_ours(args, rank, world, local_rank):
         barrier()
         return "bit-exact" if int(flag.item()) == 1 else "mismatch"
 
-    bd.sdpa_allgather_mode({"epilogue": 0, "persistent": 1, "auto": 2}[args.gather_kernel])
-    uses_persistent = args.gather_kernel == "persistent" or (args.gather_kernel == "auto" and world - 1 >= 3)
     for i in range(args.warmup):
         step(i)
     barrier()
     if bd.device_status() != 0:
         raise RuntimeError("a kernel reported a device-side failure during warm-up")
-    # N > 1, fused gather: the persistent kernel with the peer push is the default; it is
-    # checked once before anything is timed and the run falls back to the kernel whose
-    # epilogue stores to the peers itself if its gathered heads are not bit-exact.
-    gather_kernel = None
-    if world > 1 and gathered is not None and not uses_persistent:
-        gather_kernel = "epilogue peer stores"
-    elif world > 1 and gathered is not None:
-        gather_kernel = "persistent kernel, peer push by spare warps"
-        pre = check_gather()
-        if pre != "bit-exact" or bd.device_status() != 0:
-            bd.sdpa_allgather_mode(0)
-            gather_kernel = f"epilogue peer stores (fallback: the persistent kernel's pre-check gave {pre})"
-            for i in range(3):
-                step(i)
-            barrier()
-
     def time_attention_kernel(iters):
         """Average device time of the attention launch alone (events on the launching stream)."""
         ke = [torch.cuda.Event(enable_timing=True) for _ in range(2 * iters)]
@@ -802,7 +784,6 @@ def run_ours(args, rank, world, local_rank):
         }
         if world > 1:
             line["gather_check"] = gather_check
-            line["gather_kernel"] = gather_kernel
             line["one_gpu_same_workload"] = one_gpu
         if world == 1:
             if not args.no_also:
@@ -920,10 +901,6 @@ def main():
                     help="RMSNorm + RoPE of Q inside the attention kernel or in the pre-pass")
     ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
-    ap.add_argument("--gather-kernel", choices=["auto", "persistent", "epilogue"], default="auto",
-                    help="N > 1, fused gather: persistent kernel whose spare warps push finished tiles to the "
-                         "peers, the one-item-per-CTA kernel whose epilogue stores to the peers, or the "
-                         "library's choice by the number of peers (persistent from three peers on)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

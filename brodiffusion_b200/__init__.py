@@ -332,14 +332,6 @@ class MultiGpu:
             self.handle = None
 
 
-def sdpa_allgather_mode(mode: int = -1) -> int:
-    """``bdattn_sdpa_allgather_mode``: 1 = persistent kernel with the peer push,
-    0 = epilogue stores by the one-item-per-CTA kernel, 2 = by the number of peers
-    (default: persistent from three peers on); returns the previous mode, any other
-    argument only queries."""
-    return int(lib().bdattn_sdpa_allgather_mode(mode))
-
-
 def rmsnorm_rope(jobs, num_heads, head_dim, *, eps=1e-6, pair_mode=ROPE_INTERLEAVED, stream=None):
     """``bdattn_rmsnorm_rope``.  jobs: list of dicts with keys x, out and
     optional gain, cos, sin, rope_row0 (torch CUDA tensors)."""

@@ -3,7 +3,6 @@
 // stream the caller passes.
 #include "../../include/bdattn.h"
 
-#include <atomic>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -141,12 +140,6 @@ int make_map_2d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
                     op, static_cast<int>(r), base, cols, rows, ld);
     return 0;
 }
-
-// Kernel of the head-sharded calls (n_peers > 0): 1 = the persistent kernel with the
-// peer push, 0 = the one-item-per-CTA kernel whose epilogue stores to the peers itself,
-// 2 = by the number of peers (persistent from three peers on).
-std::atomic<int> g_allgather_mode{2};
-constexpr int kPersistentFromPeers = 3;
 
 int round_up(int x, int m) { return (x + m - 1) / m * m; }
 
@@ -383,11 +376,7 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         L.head_dim = hd_kernel;
         L.bf16 = bf16;
         if (L.num_heads > 65535 || L.batch > 65535) return fail("%s: num_heads/batch too large", op);
-        // the head-sharded call runs on the persistent kernel, whose spare warps push
-        // finished tiles to the peers behind the computation (bdattn_sdpa_allgather_mode)
-        const int gmode = g_allgather_mode.load();
-        const bool persistent = n_peers > 0 && (gmode == 1 || (gmode == 2 && n_peers >= kPersistentFromPeers));
-        cudaError_t e = persistent ? bdattn::launch_sdpa_tc05_persistent(L, st) : bdattn::launch_sdpa_tc05(L, st);
+        cudaError_t e = bdattn::launch_sdpa_tc05(L, st);
         if (e != cudaSuccess) return cuda_fail(op, e);
         return 0;
     }
@@ -428,11 +417,6 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream) {
     return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, nullptr, stream);
-}
-
-int bdattn_sdpa_allgather_mode(int mode) {
-    if (mode < 0 || mode > 2) return g_allgather_mode.load();
-    return g_allgather_mode.exchange(mode);
 }
 
 size_t bdattn_sdpa_traced_workspace_bytes(int num_heads, int q_rows_total) {

@@ -65,9 +65,6 @@ struct SdpaLaunch {
 };
 
 cudaError_t launch_sdpa_tc05(const SdpaLaunch& L, cudaStream_t stream);
-// Persistent variant (one CTA per SM walking the work items; warps 10-11 push finished
-// tiles to the peers): used when the output also goes to other GPUs.
-cudaError_t launch_sdpa_tc05_persistent(const SdpaLaunch& L, cudaStream_t stream);
 
 // General kernel (any head_dim that is a multiple of 8 up to 256).
 struct SdpaGeneralArgs {

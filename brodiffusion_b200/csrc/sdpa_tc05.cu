@@ -38,13 +38,19 @@
 // Arithmetic follows the attention core of dit::joint_attention_traced
 // (src/dit/common.cpp:246-305): scale 1/sqrt(hd), stable softmax,
 // inv = denom > 0 ? 1/denom : 0, with FP32 scores and accumulation.
-#include "sdpa_tc05_common.cuh"
+#include "sdpa_internal.h"
+#include "tc05.cuh"
 
 namespace bdattn {
 
 namespace {
 
-using namespace sdpa_tc;
+constexpr int kBM = 128;           // query rows per tile
+constexpr int kBN = 128;           // keys per tile
+constexpr int kThreads = 384;
+constexpr int kChunkBytes = 128 * 128;  // one 64-column (128 B) x 128-row TMA box
+constexpr int kRegsSoftmax = 216;
+constexpr int kRegsOther = 64;
 
 template <int HD>
 struct Cfg {
@@ -55,6 +61,69 @@ struct Cfg {
     static constexpr int kBarBytes = 256;
     static constexpr int kSmemBytes = 2 * kQBytes + kStages * kTileBytes + kBarBytes + 1024;
 };
+
+struct TileInfo {
+    int seg;
+    int row0;
+    int valid;
+    int kbase;
+};
+
+__device__ __forceinline__ TileInfo kv_tile(const SdpaDevArgs& a, int t) {
+    TileInfo ti;
+    if (t < a.kv_tiles0) {
+        ti.seg = 0;
+        ti.row0 = t * kBN;
+        ti.valid = min(kBN, a.kv_rows[0] - ti.row0);
+        ti.kbase = ti.row0;
+    } else {
+        ti.seg = 1;
+        ti.row0 = (t - a.kv_tiles0) * kBN;
+        ti.valid = min(kBN, a.kv_rows[1] - ti.row0);
+        ti.kbase = a.kv_rows[0] + ti.row0;
+    }
+    return ti;
+}
+
+// ------------------------------------------------------- packed FP32 math
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// (d0, d1) = (a0, a1) * (b0, b1) + (c0, c1)
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1,
+                                      float c0, float c1) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rc, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "mov.b64 rc, {%6, %7};\n"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n"
+        ".reg .b64 ra, rb, rd;\n"
+        "mov.b64 ra, {%2, %3};\n"
+        "mov.b64 rb, {%4, %5};\n"
+        "add.rn.f32x2 rd, ra, rb;\n"
+        "mov.b64 {%0, %1}, rd;\n"
+        "}\n"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 // HOOKS: 0 = none; 1 = key_mask only; 2 = key_mask, bias and the per-row softmax
 // statistics (slower softmax path).

@@ -166,22 +166,6 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream);
 
-/* Which kernel the head-sharded calls (bdattn_sdpa_fwd_allgather,
- * bdattn_mgpu_sdpa_fwd_headsharded) run on, process-wide (no counterpart in the
- * reference):
- *   1  a persistent kernel, one CTA per SM, whose two spare warps copy every
- *      finished tile from the local output to the peers' copies while the
- *      attention of the following tiles runs;
- *   0  the kernel of bdattn_sdpa_fwd, whose epilogue stores each vector to the
- *      local copy and to every peer itself (the stores of a wave of CTAs leave in
- *      one burst: 0.21 of 0.97 ms per call with seven peers, little with one);
- *   2  (default) by the number of peers: 1 from three peers on, else 0 (with one
- *      peer the persistent kernel's slower steady state costs more, 4 %, than its
- *      peer push saves).
- * All give bit-identical outputs.  Returns the previous mode; any other argument
- * only queries. */
-int bdattn_sdpa_allgather_mode(int mode);
-
 /* ------------------------------------------------ several GPUs, one process
  * Set-up and completion for a caller that drives the GPUs of one node from one
  * process with one host thread per GPU (no counterpart in the reference, which

@@ -386,60 +386,52 @@ def test_query_norm_and_rope_inside_the_kernel(bd, oracle, nh, hd, axes):
     G.check(G.host(out3), ref3, what=f"fused query rope only hd={hd}")
 
 
-@pytest.mark.parametrize("mode", [1, 0])
-def test_fused_allgather_kernels_on_one_gpu_with_local_stand_in_peers(bd, oracle, mode):
+def test_fused_allgather_on_one_gpu_with_local_stand_in_peers(bd, oracle):
     """The head-sharded call (bdattn_sdpa_fwd_allgather) on ONE GPU: the "peers" are
-    three more buffers on the same device, so both kernels behind it run where only
-    one GPU is at hand - mode 1, the persistent kernel whose spare warps copy finished
-    tiles to the peers, and mode 0, the epilogue that stores to the peers itself.
-    Every copy must equal the plain call bit for bit; shapes cover several work items
-    per CTA (more items than SMs), two query segments with a ragged tail, batch 2,
-    and the hooks that change which warps do the peer stores."""
-    prev = bd.sdpa_allgather_mode(mode)
-    try:
-        nh, hd, B, txt, img = 4, 128, 2, 200, 5000          # (1 + 20) query CTAs x 4 heads x 2 = 168 items > 148 SMs
-        L, D = txt + img, nh * hd
-        gen = torch.Generator(device="cuda").manual_seed(4242 + mode)
-        q, k, v = (torch.randn(B, L, D, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
-        seg = lambda t: [t[:, :txt], t[:, txt:]]
-        ref = torch.empty_like(q)
-        bd.sdpa_fwd(seg(q), seg(k), seg(v), seg(ref), nh)
-        copies = [torch.full_like(q, float("nan")) for _ in range(4)]
-        ptrs = lambda row0: [c[:, row0:].data_ptr() for c in copies[1:]]
-        bd.sdpa_fwd(seg(q), seg(k), seg(v), seg(copies[0]), nh, peer_out_ptrs=[ptrs(0), ptrs(txt)])
-        assert bd.device_status() == 0
-        for i, c in enumerate(copies):
-            assert torch.equal(c, ref), f"copy {i} differs from the plain call (mode {mode})"
-        # against the oracle on a few rows of batch item 1 (the persistent kernel is not
-        # otherwise reached by the single-GPU parity tests)
-        rows = G.boundary_rows(L, extra=4)[:10]
-        o = oracle.sdpa(G.host(q[1]), G.host(k[1]), G.host(v[1]), nh, rows=rows)
-        G.check(G.host(copies[2][1])[rows], o, what="gathered copy vs oracle")
-        # causal + key mask, one segment, head dim 64: hooks path of both kernels
-        nh2, hd2, L2 = 3, 64, 700
-        q2, k2, v2 = (torch.randn(L2, nh2 * hd2, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
-        km = torch.ones(L2, device="cuda")
-        km[100:140] = 0
-        ref2 = torch.empty_like(q2)
-        bd.sdpa_fwd(q2, k2, v2, ref2, nh2, mask_mode=bd.MASK_CAUSAL, key_mask=km)
-        c2 = [torch.full_like(q2, float("nan")) for _ in range(3)]
-        bd.sdpa_fwd(q2, k2, v2, c2[0], nh2, mask_mode=bd.MASK_CAUSAL, key_mask=km,
-                    peer_out_ptrs=[[c.data_ptr() for c in c2[1:]]])
-        # per-key scale vectors: warps 10-11 scale K / V tiles, the softmax warps store to the peers
-        ks = torch.ones(L2, device="cuda")
-        ks[:128] = 0.5
-        ref3 = torch.empty_like(q2)
-        bd.sdpa_fwd(q2, k2, v2, ref3, nh2, key_scale=ks, val_scale=ks)
-        c3 = [torch.full_like(q2, float("nan")) for _ in range(3)]
-        bd.sdpa_fwd(q2, k2, v2, c3[0], nh2, key_scale=ks, val_scale=ks,
-                    peer_out_ptrs=[[c.data_ptr() for c in c3[1:]]])
-        assert bd.device_status() == 0
-        for c in c2:
-            assert torch.equal(c, ref2)
-        for c in c3:
-            assert torch.equal(c, ref3)
-    finally:
-        bd.sdpa_allgather_mode(prev)
+    three more buffers on the same device, so the peer-store epilogue runs where only
+    one GPU is at hand.  Every copy must equal the plain call bit for bit; shapes
+    cover more CTAs than SMs, two query segments with a ragged tail, batch 2, and the
+    masked and scaled instantiations."""
+    nh, hd, B, txt, img = 4, 128, 2, 200, 5000          # (1 + 20) query CTAs x 4 heads x 2 = 168 items > 148 SMs
+    L, D = txt + img, nh * hd
+    gen = torch.Generator(device="cuda").manual_seed(4242)
+    q, k, v = (torch.randn(B, L, D, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
+    seg = lambda t: [t[:, :txt], t[:, txt:]]
+    ref = torch.empty_like(q)
+    bd.sdpa_fwd(seg(q), seg(k), seg(v), seg(ref), nh)
+    copies = [torch.full_like(q, float("nan")) for _ in range(4)]
+    ptrs = lambda row0: [c[:, row0:].data_ptr() for c in copies[1:]]
+    bd.sdpa_fwd(seg(q), seg(k), seg(v), seg(copies[0]), nh, peer_out_ptrs=[ptrs(0), ptrs(txt)])
+    assert bd.device_status() == 0
+    for i, c in enumerate(copies):
+        assert torch.equal(c, ref), f"copy {i} differs from the plain call"
+    # against the oracle on a few rows of batch item 1
+    rows = G.boundary_rows(L, extra=4)[:10]
+    o = oracle.sdpa(G.host(q[1]), G.host(k[1]), G.host(v[1]), nh, rows=rows)
+    G.check(G.host(copies[2][1])[rows], o, what="gathered copy vs oracle")
+    # causal + key mask, one segment, head dim 64
+    nh2, hd2, L2 = 3, 64, 700
+    q2, k2, v2 = (torch.randn(L2, nh2 * hd2, device="cuda", dtype=torch.bfloat16, generator=gen) for _ in range(3))
+    km = torch.ones(L2, device="cuda")
+    km[100:140] = 0
+    ref2 = torch.empty_like(q2)
+    bd.sdpa_fwd(q2, k2, v2, ref2, nh2, mask_mode=bd.MASK_CAUSAL, key_mask=km)
+    c2 = [torch.full_like(q2, float("nan")) for _ in range(3)]
+    bd.sdpa_fwd(q2, k2, v2, c2[0], nh2, mask_mode=bd.MASK_CAUSAL, key_mask=km,
+                peer_out_ptrs=[[c.data_ptr() for c in c2[1:]]])
+    # per-key scale vectors together with the peer stores
+    ks = torch.ones(L2, device="cuda")
+    ks[:128] = 0.5
+    ref3 = torch.empty_like(q2)
+    bd.sdpa_fwd(q2, k2, v2, ref3, nh2, key_scale=ks, val_scale=ks)
+    c3 = [torch.full_like(q2, float("nan")) for _ in range(3)]
+    bd.sdpa_fwd(q2, k2, v2, c3[0], nh2, key_scale=ks, val_scale=ks,
+                peer_out_ptrs=[[c.data_ptr() for c in c3[1:]]])
+    assert bd.device_status() == 0
+    for c in c2:
+        assert torch.equal(c, ref2)
+    for c in c3:
+        assert torch.equal(c, ref3)
 
 
 # --------------------------------------------------------------- edge cases
