@@ -524,7 +524,7 @@ def run_ours(args, rank, world, local_rank):
     def check_gather():
         """One more step on set 0, then rank 0 recomputes the heads rank 1 owns from
         rank 1's own inputs (regenerated from its seed) with the plain, unsharded launch
-        and compares them bit for bit with its gathered copy.  Every rank gets the verdict."""
+        and compares them bit for bit with its gathered copy.  Every rank gets the result."""
         step(0)
         barrier()
         flag = torch.zeros(1, device=dev, dtype=torch.int32)

@@ -17,7 +17,9 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_ref", "libref.so")
-REF_TREE = os.environ.get("BRODIFFUSION_REF", "/root/reference")
+# the brodiffusion source tree: BRODIFFUSION_REF, else the directory named reference beside this repository
+REF_TREE = os.environ.get("BRODIFFUSION_REF",
+                          os.path.abspath(os.path.join(_HERE, "..", "..", "reference")))
 _lib = None
 _fp = C.POINTER(C.c_float)
 
