@@ -67,11 +67,11 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// (cols, rows, batch) row-major 16-bit tensor, box = 64 columns x box_rows rows,
-// 128-byte swizzle, zero fill outside the tensor.
+// (cols, rows, batch) row-major 16-bit tensor, box = box_cols columns x box_rows rows,
+// 128-byte swizzle (or 64-byte, or none when swizzle_bytes is 0), zero fill outside the tensor.
 int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, long long cols,
                 long long rows, long long batch, long long ld, long long batch_stride,
-                int box_rows, int box_cols = 64, bool swizzle = true) {
+                int box_rows, int box_cols = 64, int swizzle_bytes = 128) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return fail("%s: cuTensorMapEncodeTiled is not available from the driver", op);
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
@@ -82,7 +82,8 @@ int make_map_3d(const char* op, CUtensorMap* m, const void* base, bool bf16, lon
     cuuint32_t estr[3] = {1, 1, 1};
     CUresult r = fn(m, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3,
                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                         : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
@@ -629,8 +630,8 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     a.eps = eps; a.sz_in = sz_in; a.w_in = w_in; a.sz_out = sz_out;
     const long long D = static_cast<long long>(num_heads) * 32;
     CUtensorMap tq, tk, tv, to;
-    // output: one 16-token x 32-row piece per warp and store, plain row-major in shared memory
-    if (make_map_3d(op, &to, out, true, n_tokens, D, batch, ld, a.batch_stride, 32, 16, false)) return -1;
+    // output: one 32-token x 32-row piece per warp and store, 64-byte rows under the 64-byte swizzle
+    if (make_map_3d(op, &to, out, true, n_tokens, D, batch, ld, a.batch_stride, 32, 32, 64)) return -1;
     if (make_map_3d(op, &tq, q, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tk, k, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;
     if (make_map_3d(op, &tv, v, true, n_tokens, D, batch, ld, a.batch_stride, 32)) return -1;

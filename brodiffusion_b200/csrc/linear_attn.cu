@@ -15,8 +15,9 @@
 //   reduce  warps -> CTA in shared memory, CTA -> cluster through distributed
 //           shared memory (no global scratch);
 //   pass B  Q chunks -> out = [S; z] relu(Q) with the state rounded to BF16
-//           (FP32 accumulation), division by the z row, BF16 tile staged in
-//           shared memory and written by TMA store.
+//           (FP32 accumulation), division by the z row; every warp stages its
+//           own 32-row x 32-token BF16 piece of a 256-token item in shared memory
+//           and sends it off with its own TMA store.
 // Tiles arrive by TMA (64-token x 32-row boxes, 128-byte swizzle) into a ring
 // shared by both passes and fed by a dedicated producer warp (full / empty
 // mbarriers, no CTA-wide barrier in the loops), so the first Q chunks are in
@@ -37,17 +38,19 @@ constexpr int kLaChunk = 128;                 // tokens per ring item
 constexpr int kLaMaxStages = 8;               // ring of 16 KB items: 8 with one CTA per SM, 3 when two share it
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
-constexpr int kLaPieceBytes = 32 * 16 * 2;    // output piece of one warp and chunk: 32 rows x 16 tokens, row-major
+constexpr int kLaPieceBytes = 32 * 32 * 2;    // output piece of one warp and item: 32 rows x 32 tokens (64-byte rows)
 constexpr int kLaState = 33 * 32;             // [S; z] floats
 constexpr int kLaStLd = 40;                   // row stride of the state tile in shared memory: the fragment
                                               // loads of the apply pass (rows over g, columns over q4) then
                                               // meet at most two to a bank instead of eight
 
 struct LaSmem {
-    float partial[kLaWarps][kLaState];
+    union {
+        float partial[kLaWarps][kLaState];                          // reduction between the passes
+        alignas(1024) uint8_t out_stage[kLaWarps][2][kLaPieceBytes];  // pass B: two output pieces per warp
+    };
     float local_state[kLaState];
     float state[48 * kLaStLd];   // rows 33..47 zero
-    alignas(1024) uint8_t out_stage[kLaWarps][2][kLaPieceBytes];   // per warp: two 32-row x 16-token output pieces
     uint64_t full[kLaMaxStages];
     uint64_t empty[kLaMaxStages];
     alignas(1024) uint8_t ring[1][kLaSlotBytes];   // a.stages items follow (dynamic shared memory)
@@ -125,6 +128,11 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int kLaStages = a.stages;
     uint8_t* const ring_base = &sm.ring[0][0];     // a.stages items of kLaSlotBytes
 
+    // Programmatic dependent launch: the next kernel of the stream (if it was
+    // launched with the same attribute) may become resident as CTAs of this one
+    // retire and run its own set-up; its griddepcontrol.wait holds it back until
+    // this grid has completed and its writes are visible.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     if (tid == 0) {
         for (int s = 0; s < kLaStages; ++s) {
             mbar_init(&sm.full[s], 1);
@@ -133,6 +141,15 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         fence_mbar_init();
     }
     for (int i = tid; i < 48 * kLaStLd; i += kLaThreads) sm.state[i] = 0.0f;
+    if (tid == kLaWarps * 32) {
+        tma_prefetch_desc(&tmK);
+        tma_prefetch_desc(&tmV);
+        tma_prefetch_desc(&tmQ);
+        tma_prefetch_desc(&tmO);
+    }
+    // Everything above touched shared memory only.  No global read or write of this
+    // kernel is issued before the preceding kernel of the stream has completed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     __syncthreads();
 
     if (warp == kLaWarps) {
@@ -326,27 +343,27 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 ah[mt][ks][r] = pack2<true>(x0, x1);
             }
 
+    // Warp w owns tokens [32 w, 32 w + 32) of a 256-token item (half of box w / 2)
+    // and stages and stores that piece by itself (TMA store issued by its lane 0),
+    // so no barrier of the CTA sits between items and the warps drift apart, which
+    // hides the latency chain of a piece (tile load, MMAs, reciprocal, packing).
+    // Two pieces per warp alternate: before a piece is overwritten, the store that
+    // last read it has finished reading.  The pieces lie where the partial states
+    // of the reduction were: every warp is past the barrier that followed it.
     for (int it = n_mine; it < n_items; ++it) {
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
-#pragma unroll 1
-        for (int sub = 0; sub < 2; ++sub) {
-            const int cidx = 2 * (it - n_mine) + sub;     // 128-token chunk of this CTA
-            if (cidx >= n_mine) break;
-            // Every warp stages and stores its own 32-row x 16-token piece (TMA store
-            // issued by its lane 0), so no barrier of the CTA sits between chunks and
-            // the warps drift apart, which hides the latency chain of a chunk (tile
-            // load, MMAs, reciprocal, packing).  Two pieces per warp alternate: before
-            // a piece is overwritten, the store that last read it has finished reading.
-            uint8_t* stage = sm.out_stage[warp][cidx & 1];
+        const int bi = it - n_mine;
+        if (2 * bi + (warp >> 2) < n_mine) {          // this warp's 128-token chunk exists
+            uint8_t* stage = sm.out_stage[warp][bi & 1];
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
             if (ok) {
-                const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (2 * sub + box) * kLaBoxBytes;
+                const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (warp >> 1) * kLaBoxBytes;
 #pragma unroll
-                for (int nt = 0; nt < 2; ++nt) {
+                for (int nt = 0; nt < 4; ++nt) {
                     uint32_t b[4];
-                    ldsm_x4_trans(qb + swz(lane, chunk0 + nt), b[0], b[1], b[2], b[3]);
+                    ldsm_x4_trans(qb + swz(lane, (warp & 1) * 4 + nt), b[0], b[1], b[2], b[3]);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
                     float o[3][4];
@@ -365,21 +382,24 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                     const float den1 = __shfl_sync(0xffffffffu, o[2][1], q4);
                     const float r0 = 1.0f / (den0 + a.eps);
                     const float r1 = 1.0f / (den1 + a.eps);
-                    // row-major piece, 32 bytes per row: lanes g = 0..7 of a store fall
-                    // into eight different 32-byte rows, q4 into its words: no conflicts
-                    uint8_t* sp = stage + (nt * 8 + q4 * 2) * 2;
+                    // 64-byte rows under the 64-byte swizzle of the store's tensor map
+                    // (16-byte chunk c of row r sits at chunk c ^ ((r >> 1) & 3)): the
+                    // eight rows and four words of one store fall into 32 different banks
+                    uint8_t* sp = stage + q4 * 4;
 #pragma unroll
                     for (int mt = 0; mt < 2; ++mt) {
                         const int i0 = mt * 16 + g;
-                        *reinterpret_cast<uint32_t*>(sp + i0 * 32) = pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
-                        *reinterpret_cast<uint32_t*>(sp + (i0 + 8) * 32) = pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
+                        *reinterpret_cast<uint32_t*>(sp + i0 * 64 + (((nt ^ (i0 >> 1)) & 3) << 4)) =
+                            pack2<true>(o[mt][0] * r0, o[mt][1] * r1);
+                        *reinterpret_cast<uint32_t*>(sp + (i0 + 8) * 64 + (((nt ^ ((i0 + 8) >> 1)) & 3) << 4)) =
+                            pack2<true>(o[mt][2] * r0, o[mt][3] * r1);
                     }
                 }
             }
             fence_proxy_async_smem();
             __syncwarp();
             if (ok && lane == 0) {
-                const int tok = (c_begin + cidx) * kLaChunk + box * 64 + (warp & 3) * 16;
+                const int tok = (c_begin + 2 * bi) * kLaChunk + warp * 32;
                 if (tok < a.n_tokens) tma_store_3d(&tmO, stage, tok, row0, batch);
                 tma_store_commit();
             }
@@ -408,13 +428,16 @@ cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, 
     cfg.blockDim = dim3(kLaThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = static_cast<unsigned>(cluster_size);
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    // set-up of this launch may overlap the tail of the kernel before it (see the kernel's first lines)
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.numAttrs = 2;
     return cudaLaunchKernelEx(&cfg, linear_attn_kernel, tmQ, tmK, tmV, tmO, a);
 }
 

@@ -101,6 +101,40 @@ def test_capture_and_inject_state(bd, oracle):
     G.check(out, ref, what="inject")
 
 
+def test_back_to_back_launches_see_each_others_results(bd, oracle):
+    """The kernel is launched with programmatic stream serialisation: its set-up
+    may overlap the tail of the kernel before it.  Launches that depend on one
+    another (the second reads the first's output as its queries; the third
+    overwrites the buffer the second read) must give what separately synchronised
+    launches give, every time."""
+    nh, N = 70, 1024
+    D = nh * 32
+    q, k, v = (synth.activations((2, D, N), 6400 + i) for i in range(3))
+    tq, tk, tv = G.dev(q), G.dev(k), G.dev(v)
+    o1, o2 = torch.empty_like(tq), torch.empty_like(tq)
+    # separately synchronised
+    bd.linear_attn_relu_fwd(tq, tk, tv, o1, nh, 32)
+    torch.cuda.synchronize()
+    bd.linear_attn_relu_fwd(o1, tk, tv, o2, nh, 32)
+    torch.cuda.synchronize()
+    want1, want2 = o1.clone(), o2.clone()
+    bd.linear_attn_relu_fwd(tq, tv, tk, o1, nh, 32)
+    torch.cuda.synchronize()
+    want3 = o1.clone()
+    for _ in range(20):
+        o1.fill_(float("nan"))
+        o2.fill_(float("nan"))
+        bd.linear_attn_relu_fwd(tq, tk, tv, o1, nh, 32)
+        bd.linear_attn_relu_fwd(o1, tk, tv, o2, nh, 32)     # reads o1
+        bd.linear_attn_relu_fwd(tq, tv, tk, o1, nh, 32)     # overwrites o1
+        torch.cuda.synchronize()
+        assert torch.equal(o2, want2)
+        assert torch.equal(o1, want3)
+    assert bd.device_status() == 0
+    ref = oracle.sana_linear_attn(q[0], k[0], v[0], nh, 32)
+    G.check(G.host(want1)[0], ref, what="first launch")
+
+
 def test_all_negative_keys_give_zero(bd):
     nh, N = 2, 128
     q = synth.activations((nh * 32, N), 6301)
