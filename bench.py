@@ -165,8 +165,9 @@ def workload_config(args, world):
             "head_dim": HD, "heads_per_gpu": NH // world,
             "step": step_text(args.q_norm == "fused", world),
             "gather": "none" if world == 1 else
-                      ("fused peer stores in the attention epilogue + symmetric-memory barrier"
-                       if args.gather == "fused" else "nccl all-gather"),
+                      ("fused into the attention epilogue (stores to the switch's multicast address, or "
+                       "to every peer) + symmetric-memory barrier"
+                       if args.gather.startswith("fused") else "nccl all-gather"),
             "l2": "GPU arm: steps rotate over input sets that together exceed the 126 MB L2; "
                   "host arm: inputs are read from host memory"}
 
@@ -460,15 +461,24 @@ def run_ours(args, rank, world, local_rank):
     # N > 1: the head outputs are gathered either by the attention kernel itself
     # (epilogue stores into every rank's replica through symmetric memory) or,
     # with --gather nccl, by an in-place NCCL all-gather of a head-major staging tensor.
-    gathered, peer_ptrs = None, None
+    gathered, peer_ptrs, mc_ptrs = None, None, None
+    gather_path = "none" if world == 1 else "nccl all-gather"
     config = workload_config(args, world)
-    if world > 1 and args.gather == "fused":
+    if world > 1 and args.gather.startswith("fused"):
         try:
             gathered = headshard.GatheredOutput(batch, L, NH, HD, torch.bfloat16, dev)
             peer_ptrs = [gathered.peer_ptrs(0), gathered.peer_ptrs(txt)]
+            gather_path = "plain stores to every peer"
+            # every rank must take the same path: the multicast address is used only if all have one
+            have_mc = torch.tensor([1 if gathered.multicast_ptr(0) else 0], device=dev, dtype=torch.int32)
+            dist.all_reduce(have_mc, op=dist.ReduceOp.MIN)
+            if args.gather == "fused" and int(have_mc.item()) == 1:
+                mc_ptrs = [gathered.multicast_ptr(0), gathered.multicast_ptr(txt)]
+                peer_ptrs = None
+                gather_path = "multimem.st to the switch's multicast address"
         except Exception as e:      # symmetric memory unavailable: NCCL path
-            gathered = None
-            config["gather"] = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
+            gathered, peer_ptrs, mc_ptrs = None, None, None
+            gather_path = f"nccl all-gather (symmetric memory unavailable: {type(e).__name__})"
     staging = torch.empty(headshard.staging_shape(world, batch, L, NH, HD), device=dev,
                           dtype=torch.bfloat16)
     out = gathered.local if gathered is not None else staging[rank]
@@ -500,7 +510,8 @@ def run_ours(args, rank, world, local_rank):
         qq = q if q_fused else (qr if qr_ is None else qr_)
         bd.sdpa_fwd([qq[:, :txt], qq[:, txt:]], [kr_[:, :txt], kr_[:, txt:]], [v[:, :txt], v[:, txt:]],
                     [out_[:, :txt], out_[:, txt:]], nh_l if heads is None else heads, q_norm=q_norm,
-                    peer_out_ptrs=peer_ptrs if peers else None)
+                    peer_out_ptrs=peer_ptrs if peers else None,
+                    multicast_out_ptrs=mc_ptrs if peers else None)
 
     def gather():
         if gathered is not None:
@@ -537,7 +548,15 @@ def run_ours(args, rank, world, local_rank):
             torch.cuda.synchronize()
             c0 = headshard.head_range(NH, world, 1)[0] * HD
             theirs = gathered.full[:, :, c0:c0 + d_l] if gathered is not None else staging[1]
-            flag[0] = 1 if torch.equal(theirs, o_out) else 0
+            same = torch.equal(theirs, o_out)
+            # and this rank's own columns of its own copy (they too arrive through the gather)
+            mq, mk, mv = sets[0]
+            norm_rope(mq, mk, kr_=o_kr, qr_=o_qr)
+            attention(mq, mv, out_=o_out, kr_=o_kr, qr_=o_qr, peers=False)
+            torch.cuda.synchronize()
+            mine = gathered.full[:, :, :d_l] if gathered is not None else staging[0]
+            same = same and torch.equal(mine, o_out)
+            flag[0] = 1 if same else 0
             del oq, ok_, ov, o_kr, o_qr, o_out
         dist.broadcast(flag, src=0)
         barrier()
@@ -784,6 +803,7 @@ def run_ours(args, rank, world, local_rank):
         }
         if world > 1:
             line["gather_check"] = gather_check
+            line["gather_path"] = gather_path
             line["one_gpu_same_workload"] = one_gpu
         if world == 1:
             if not args.no_also:
@@ -899,7 +919,7 @@ def main():
                     help="skip the other configurations and the library baselines (1 GPU)")
     ap.add_argument("--q-norm", choices=["fused", "prepass"], default=None,
                     help="RMSNorm + RoPE of Q inside the attention kernel or in the pre-pass")
-    ap.add_argument("--gather", choices=["fused", "nccl"], default="fused",
+    ap.add_argument("--gather", choices=["fused", "fused-peer", "nccl"], default="fused",
                     help="N > 1: how the head outputs are gathered")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -132,6 +132,8 @@ def lib():
         L.bdattn_sdpa_fwd.argtypes = [C.POINTER(SdpaParams), C.c_void_p]
         L.bdattn_sdpa_fwd_allgather.argtypes = [C.POINTER(SdpaParams), C.POINTER(C.c_void_p),
                                                 C.POINTER(C.c_void_p), C.c_int, C.c_void_p]
+        L.bdattn_sdpa_fwd_allgather_multicast.argtypes = [C.POINTER(SdpaParams), C.c_void_p, C.c_void_p,
+                                                          C.c_void_p]
         L.bdattn_mgpu_init.argtypes = [C.POINTER(C.c_void_p), C.POINTER(C.c_int), C.c_int]
         L.bdattn_mgpu_destroy.argtypes = [C.c_void_p]
         L.bdattn_mgpu_size.argtypes = [C.c_void_p]
@@ -227,12 +229,14 @@ def device_status(clear: bool = True) -> int:
 
 def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key_scale=None,
              val_scale=None, softmax_scale=0.0, num_kv_heads=0, q_norm=None, stream=None,
-             peer_out_ptrs=None, _trace=None, _mgpu=None):
+             peer_out_ptrs=None, multicast_out_ptrs=None, _trace=None, _mgpu=None):
     """``bdattn_sdpa_fwd``.  q/out and k/v are a tensor or a list of one or two
     tensors (row segments attended as if concatenated); tensors are
     (rows, nh*hd) or (B, rows, nh*hd) torch CUDA tensors.
     ``peer_out_ptrs`` (list per output segment of lists of raw device pointers
-    on other GPUs) selects ``bdattn_sdpa_fwd_allgather``."""
+    on other GPUs) selects ``bdattn_sdpa_fwd_allgather``; ``multicast_out_ptrs``
+    (one NVLink multicast address per output segment) selects
+    ``bdattn_sdpa_fwd_allgather_multicast``."""
     qs = list(q) if isinstance(q, (list, tuple)) else [q]
     os_ = list(out) if isinstance(out, (list, tuple)) else [out]
     ks = list(k) if isinstance(k, (list, tuple)) else [k]
@@ -288,6 +292,10 @@ def sdpa_fwd(q, k, v, out, num_heads, *, mask_mode=MASK_NONE, key_mask=None, key
         arr = (C.c_void_p * len(replica_ptrs))(*replica_ptrs)
         _check(lib().bdattn_mgpu_sdpa_fwd_headsharded(ctx, rank, C.byref(p), arr, replica_ld, replica_bs,
                                                       total_heads, _stream(stream)))
+        return
+    if multicast_out_ptrs:
+        m1 = multicast_out_ptrs[1] if len(multicast_out_ptrs) > 1 else None
+        _check(lib().bdattn_sdpa_fwd_allgather_multicast(C.byref(p), multicast_out_ptrs[0], m1, _stream(stream)))
         return
     if peer_out_ptrs:
         n = len(peer_out_ptrs[0])

@@ -247,7 +247,7 @@ int bdattn_device_status(int* status, int clear) {
 
 static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* const* peer_o0,
                          void* const* peer_o1, int n_peers, const bdattn_trace_params* tr,
-                         bdattn_stream_t stream) {
+                         bdattn_stream_t stream, void* const* mc_o = nullptr) {
     if (p == nullptr) return fail("%s: params is null", op);
     if (n_peers < 0 || n_peers > 8) return fail("%s: n_peers must be in [0, 8]", op);
     if (require_sm100(op)) return -1;
@@ -371,6 +371,13 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
                 a.o_peer[1][i] = peer_o1[i];
             }
         }
+        if (mc_o != nullptr) {
+            for (int s = 0; s < p->n_q_seg; ++s) {
+                if (mc_o[s] == nullptr || !aligned16(mc_o[s]))
+                    return fail("%s: multicast output of segment %d is null or not 16-byte aligned", op, s);
+                a.o_mc[s] = mc_o[s];
+            }
+        }
         L.q_ctas = a.q_ctas0 + q_ctas1;
         L.num_heads = p->num_heads;
         L.batch = p->batch;
@@ -382,7 +389,7 @@ static int sdpa_fwd_impl(const char* op, const bdattn_sdpa_params* p, void* cons
         return 0;
     }
 
-    if (n_peers > 0) return fail("%s: the fused all-gather needs head_dim <= 128", op);
+    if (n_peers > 0 || mc_o != nullptr) return fail("%s: the fused all-gather needs head_dim <= 128", op);
     if (tr != nullptr) return fail("%s: traced attention needs head_dim <= 128", op);
     bdattn::SdpaGeneralArgs g;
     std::memset(&g, 0, sizeof(g));
@@ -418,6 +425,12 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream) {
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream) {
     return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather", p, peer_o0, peer_o1, n_peers, nullptr, stream);
+}
+
+int bdattn_sdpa_fwd_allgather_multicast(const bdattn_sdpa_params* p, void* mc_o0, void* mc_o1,
+                                        bdattn_stream_t stream) {
+    void* mc[2] = {mc_o0, mc_o1};
+    return sdpa_fwd_impl("bdattn_sdpa_fwd_allgather_multicast", p, nullptr, nullptr, 0, nullptr, stream, mc);
 }
 
 size_t bdattn_sdpa_traced_workspace_bytes(int num_heads, int q_rows_total) {

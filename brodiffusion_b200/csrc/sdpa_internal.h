@@ -46,12 +46,10 @@ struct SdpaDevArgs {
     // these peer buffers (other GPUs' copies of the output tensor), per segment.
     int n_peers;
     void* o_peer[2][8];
-    // Work items of the persistent grid (filled in by the launcher): item w covers
-    // query CTA w % item_q_ctas of head (w / item_q_ctas) % item_heads of batch item
-    // w / (item_q_ctas * item_heads).
-    int n_items;
-    int item_q_ctas;
-    int item_heads;
+    // The same through the NVSwitch: when set, o_mc[seg] is the multicast address of
+    // o[seg] (one multimem.st per vector reaches every GPU's copy, this one's
+    // included) and neither o[] nor o_peer[] is stored to.
+    void* o_mc[2];
 };
 
 struct SdpaLaunch {

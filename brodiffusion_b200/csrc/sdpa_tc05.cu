@@ -520,12 +520,22 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     const uint4 w = *reinterpret_cast<const uint4*>(stg + r * (HD * 2) + ((cg ^ (r & (kRowChunks - 1))) << 4));
                     const long long off = 2 * (static_cast<long long>(batch) * o_bs + static_cast<long long>(rs) * o_ld +
                                                static_cast<long long>(head) * a.hd_out + cg * 8);
-                    *reinterpret_cast<uint4*>(obase + off) = w;
-                    // fused all-gather: the same vector goes to every peer's copy of the
-                    // output (plain stores over NVLink; no TMA, no multicast, no peer reads)
-                    for (int pi = 0; pi < a.n_peers; ++pi) {
-                        uint8_t* pb = reinterpret_cast<uint8_t*>(qseg ? a.o_peer[1][pi] : a.o_peer[0][pi]);
-                        *reinterpret_cast<uint4*>(pb + off) = w;
+                    uint8_t* const mc = reinterpret_cast<uint8_t*>(qseg ? a.o_mc[1] : a.o_mc[0]);
+                    if (mc != nullptr) {
+                        // fused all-gather through the switch: one store to the multicast
+                        // address lands in every GPU's copy of the output, this one's included
+                        asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};"
+                                     ::"l"(mc + off), "f"(__uint_as_float(w.x)), "f"(__uint_as_float(w.y)),
+                                       "f"(__uint_as_float(w.z)), "f"(__uint_as_float(w.w))
+                                     : "memory");
+                    } else {
+                        *reinterpret_cast<uint4*>(obase + off) = w;
+                        // fused all-gather: the same vector goes to every peer's copy of the
+                        // output (plain stores over NVLink; no TMA, no peer reads)
+                        for (int pi = 0; pi < a.n_peers; ++pi) {
+                            uint8_t* pb = reinterpret_cast<uint8_t*>(qseg ? a.o_peer[1][pi] : a.o_peer[0][pi]);
+                            *reinterpret_cast<uint4*>(pb + off) = w;
+                        }
                     }
                 }
             }

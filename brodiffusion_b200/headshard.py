@@ -66,8 +66,8 @@ def project_staged(staging, w_out, bias=None):
 class GatheredOutput:
     """Full (B, L, D) attention output replicated on every rank in symmetric
     memory, for the fused all-gather (``bdattn_sdpa_fwd_allgather``): each rank's
-    attention kernel stores its head columns into every replica through
-    peer-mapped pointers, so after ``barrier()`` every rank holds the reference
+    attention kernel stores its head columns into every replica (through
+    peer-mapped pointers, or once through the switch's multicast address), so after ``barrier()`` every rank holds the reference
     layout (B, L, num_heads * head_dim) without a staging copy or an NCCL call.
     """
 
@@ -86,12 +86,22 @@ class GatheredOutput:
         # this rank's head columns inside its own replica
         self.local = self.full[:, :, self.col0:self.h1 * head_dim]
         self.peer_bases = [int(self.handle.buffer_ptrs[r]) for r in range(self.world) if r != self.rank]
+        # NVLink multicast address of the replicas (0 when the group has no switch multicast)
+        self.multicast_base = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def peer_ptrs(self, row0=0):
         """Peer addresses of element (0, row0, first own column)."""
         D = self.full.shape[2]
         off = (row0 * D + self.col0) * self.elem
         return [b + off for b in self.peer_bases]
+
+    def multicast_ptr(self, row0=0):
+        """Multicast address of element (0, row0, first own column): a store to it
+        lands in every rank's replica.  None without switch multicast."""
+        if not self.multicast_base:
+            return None
+        D = self.full.shape[2]
+        return self.multicast_base + (row0 * D + self.col0) * self.elem
 
     def barrier(self):
         """Stream-ordered cross-GPU barrier: once it has passed on this rank's

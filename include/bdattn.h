@@ -159,12 +159,24 @@ int bdattn_sdpa_fwd(const bdattn_sdpa_params* p, bdattn_stream_t stream);
  * symmetric memory).  The epilogue writes every output vector to the local
  * copy and to all n_peers (<= 8) peer copies with plain 16-byte stores over
  * NVLink, so the transfer overlaps the attention of later tiles and no
- * staging or NCCL call is needed; the kernel uses no TMA multicast and never
- * reads peer memory.  The caller orders the consumers: a cross-GPU barrier
+ * staging or NCCL call is needed; the kernel never reads peer memory.  The caller orders the consumers: a cross-GPU barrier
  * after the call (all ranks' kernels complete) before any rank reads the
  * gathered tensor.  head_dim 64 or 128 only. */
 int bdattn_sdpa_fwd_allgather(const bdattn_sdpa_params* p, void* const* peer_o0, void* const* peer_o1,
                               int n_peers, bdattn_stream_t stream);
+
+/* The same gather through the NVSwitch.  mc_o0 (and mc_o1 for the second query
+ * segment) is the MULTICAST address of the location p->o[] names: an address of
+ * an NVLink multicast object to which every GPU of the group has bound its copy
+ * of the output at the same offset (torch symmetric memory's multicast_ptr, or
+ * cuMulticastCreate / cuMulticastBindMem / cuMemMap by the caller).  The epilogue
+ * issues one multimem.st per 16-byte vector; the switch delivers it to every
+ * copy, the caller's own included, so each GPU sends its head columns once
+ * instead of once per peer and p->o[] itself is not stored to.  Ordering as
+ * above: a cross-GPU barrier after the call before any rank reads.  The caller
+ * keeps every rank of the group alive while a multicast object is bound. */
+int bdattn_sdpa_fwd_allgather_multicast(const bdattn_sdpa_params* p, void* mc_o0, void* mc_o1,
+                                        bdattn_stream_t stream);
 
 /* ------------------------------------------------ several GPUs, one process
  * Set-up and completion for a caller that drives the GPUs of one node from one
