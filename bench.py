@@ -532,6 +532,23 @@ def run_ours(args, rank, world, local_rank):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def check_status(where):
+        """A device-side failure on any rank ends the run on every rank at the same point:
+        all of them finish their streams, leave the process group together and only then
+        raise, so that no rank goes away while the others still run kernels that store
+        through the multicast object its memory is bound to."""
+        bad = 1 if bd.device_status() != 0 else 0
+        if world > 1:
+            t = torch.tensor([bad], device=dev, dtype=torch.int32)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            bad = int(t.item())
+        if bad:
+            if world > 1:
+                torch.cuda.synchronize()
+                dist.barrier()
+                dist.destroy_process_group()
+            raise RuntimeError(f"a kernel reported a device-side failure {where}")
+
     def check_gather():
         """One more step on set 0, then rank 0 recomputes the heads rank 1 owns from
         rank 1's own inputs (regenerated from its seed) with the plain, unsharded launch
@@ -565,8 +582,7 @@ def run_ours(args, rank, world, local_rank):
     for i in range(args.warmup):
         step(i)
     barrier()
-    if bd.device_status() != 0:
-        raise RuntimeError("a kernel reported a device-side failure during warm-up")
+    check_status("during warm-up")
     def time_attention_kernel(iters):
         """Average device time of the attention launch alone (events on the launching stream)."""
         ke = [torch.cuda.Event(enable_timing=True) for _ in range(2 * iters)]
@@ -613,8 +629,7 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         region_ms = [float(x) for x in t.tolist()]
     ms = statistics.median(region_ms)
-    if bd.device_status() != 0:
-        raise RuntimeError("a kernel reported a device-side failure during the timed region")
+    check_status("during the timed region")
 
     # the same kernel again, now in the sustained power state
     q, k, v = sets[0]
@@ -766,8 +781,7 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
-    if bd.device_status() != 0:
-        raise RuntimeError("a kernel reported a device-side failure during the end-to-end region")
+    check_status("during the end-to-end region")
 
     if rank == 0:
         line = {

@@ -1,5 +1,6 @@
 """Head-sharded attention on 2 GPUs (config 5 layout, reduced size): the NCCL
-all-gather path and the fused peer-store path against the unsharded kernel.
+all-gather path, the fused peer-store path and the fused multicast-store path
+(when the group has an NVLink multicast address) against the unsharded kernel.
 Needs two GPUs; skipped on a single-GPU box."""
 import os
 import socket
@@ -55,8 +56,20 @@ def _worker(rank, world, port, ret):
                     peer_out_ptrs=[go.peer_ptrs(0), go.peer_ptrs(txt)])
         go.barrier()
         ok_fused = torch.equal(go.full, full)
+        # (c) fused through the switch: one multimem.st per vector reaches every replica
+        have = torch.tensor([1 if go.multicast_ptr(0) else 0], device=dev, dtype=torch.int32)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        ok_mc = None
+        if int(have.item()) == 1:
+            go.full.fill_(float("nan"))
+            go.barrier()
+            bd.sdpa_fwd([ql[:, :txt], ql[:, txt:]], [kl[:, :txt], kl[:, txt:]], [vl[:, :txt], vl[:, txt:]],
+                        [lo[:, :txt], lo[:, txt:]], h1 - h0,
+                        multicast_out_ptrs=[go.multicast_ptr(0), go.multicast_ptr(txt)])
+            go.barrier()
+            ok_mc = bool(torch.equal(go.full, full))
         status = bd.device_status()
-        ret[rank] = (bool(ok_nccl), bool(ok_fused), int(status))
+        ret[rank] = (bool(ok_nccl), bool(ok_fused), int(status), ok_mc)
     finally:
         dist.destroy_process_group()
 
@@ -70,7 +83,8 @@ def test_two_gpu_head_sharding_matches_unsharded():
         ret = m.dict()
         mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
         for r in range(world):
-            ok_nccl, ok_fused, status = ret[r]
+            ok_nccl, ok_fused, status, ok_mc = ret[r]
             assert status == 0
             assert ok_nccl, f"rank {r}: NCCL all-gather result differs from the unsharded kernel"
             assert ok_fused, f"rank {r}: fused all-gather result differs from the unsharded kernel"
+            assert ok_mc is not False, f"rank {r}: multicast all-gather result differs from the unsharded kernel"

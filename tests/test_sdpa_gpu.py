@@ -496,3 +496,9 @@ def test_argument_errors_carry_the_operator_prefix(bd):
         bd.sdpa_fwd(q[:, 1:129], q[:, :128], q[:, :128], q[:, :128].clone(), 1)
     with pytest.raises(bd.BdattnError, match=r"^bdattn_sdpa_fwd: unknown mask_mode"):
         bd.sdpa_fwd(q, q, q, q.clone(), 2, mask_mode=7)
+    # the multicast gather refuses an unaligned multicast address and head dims of the general kernel
+    with pytest.raises(bd.BdattnError, match=r"^bdattn_sdpa_fwd_allgather_multicast: .*16-byte aligned"):
+        bd.sdpa_fwd(q, q, q, q.clone(), 2, multicast_out_ptrs=[q.data_ptr() + 2])
+    q192 = torch.zeros(16, 192, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(bd.BdattnError, match=r"^bdattn_sdpa_fwd_allgather_multicast: .*head_dim <= 128"):
+        bd.sdpa_fwd(q192, q192, q192, q192.clone(), 1, multicast_out_ptrs=[q192.data_ptr()])
