@@ -492,15 +492,17 @@ def run_ours(args, rank, world, local_rank):
     def norm_rope(q, k, kr_=None, qr_=None, heads=None):
         kr_ = kr if kr_ is None else kr_
         qr_ = qr if qr_ is None else qr_
+        jobs = []
         for b in range(batch):
-            jobs = [
+            jobs += [
                 dict(x=k[b, :txt], out=kr_[b, :txt], gain=gains[3], cos=cos, sin=sin, rope_row0=0),
                 dict(x=k[b, txt:], out=kr_[b, txt:], gain=gains[1], cos=cos, sin=sin, rope_row0=txt),
             ]
             if not q_fused:
                 jobs += [dict(x=q[b, :txt], out=qr_[b, :txt], gain=gains[2], cos=cos, sin=sin, rope_row0=0),
                          dict(x=q[b, txt:], out=qr_[b, txt:], gain=gains[0], cos=cos, sin=sin, rope_row0=txt)]
-            bd.rmsnorm_rope(jobs, nh_l if heads is None else heads, HD)
+        for j0 in range(0, len(jobs), 4):       # one launch takes up to four (segment, batch item) jobs
+            bd.rmsnorm_rope(jobs[j0:j0 + 4], nh_l if heads is None else heads, HD)
 
     q_norm = dict(gain=[gains[2], gains[0]], cos=cos, sin=sin, rope_row0=0) if q_fused else {}
 
@@ -519,7 +521,7 @@ def run_ours(args, rank, world, local_rank):
         elif world > 1:
             headshard.all_gather_heads(staging)
 
-    launches_per_step = batch + 1
+    launches_per_step = -(-(batch * (2 if q_fused else 4)) // 4) + 1
 
     def step(i):
         q, k, v = sets[i % n_sets]
