@@ -676,11 +676,11 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
         } else if (warp >= 10) {
             // ------------------------------------------- K / V row scaling
             // Warps 10 and 11 both walk the ring items in order (each sees every phase
-            // of the barriers it waits on) and take half of a tile's lines each.  The
-            // row factors of an item are fetched before the wait for its tile.  A tile
+            // of the barriers it waits on) and take half of a tile each.  The row
+            // factors of an item are fetched before the wait for its tile.  A tile
             // none of whose factors differs from one is passed on as it is; otherwise
-            // every 128-byte line (one row of a 64-column chunk; the swizzle permutes
-            // inside the line only) is multiplied by its row's factor.
+            // every row is multiplied by its factor (FP32 product rounded to the
+            // storage type).
             if constexpr (kScale) {
                 const int half_id = warp - 10;
                 bool ok = true;
@@ -711,46 +711,47 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     if (!ok) break;
                     if (scale_tile) {
                         uint8_t* tile = smem_kv + slot * C::kTileBytes;
-                        // lane -> 16-byte piece (lane & 7) of row 4 * g + (lane >> 3) of a chunk;
-                        // this warp takes the row groups g of its parity
-                        constexpr int kIters = 16 * C::kChunks;
-                        constexpr int kBatch = 4;       // loads of a batch are issued before its stores
-#pragma unroll 1
-                        for (int it0 = 0; it0 < kIters; it0 += kBatch) {
-                            uint4 v[kBatch];
-                            float fr[kBatch];
+                        // A lane owns whole rows (lane, lane + 32, ...: the rows whose factors it
+                        // holds).  Within a 64-column chunk a row is one 128-byte line whose 16-byte
+                        // pieces the swizzle permutes; the factor is the same for all of them, so
+                        // the pieces are walked in physical order, rotated by the lane's row so that
+                        // the 32 rows of one access fall into different banks.  The (row group,
+                        // chunk) pairs alternate between the two warps.
 #pragma unroll
-                            for (int b = 0; b < kBatch; ++b) {
-                                const int it = it0 + b;
-                                const int g = ((it & 15) << 1) + half_id;      // row group 0..31
-                                const int r = (g << 2) + (lane >> 3);
-                                const int fw = g >> 3;                          // = r >> 5, the same for the whole warp
-                                const float fsel = fw == 0 ? f[0] : (fw == 1 ? f[1] : (fw == 2 ? f[2] : f[3]));
-                                fr[b] = __shfl_sync(0xffffffffu, fsel, r & 31);
-                                v[b] = *reinterpret_cast<const uint4*>(tile + (it >> 4) * kChunkBytes + r * 128 + ((lane & 7) << 4));
-                            }
+                        for (int pi = 0; pi < 4 * C::kChunks; ++pi) {
+                            const int w = pi / C::kChunks, ch = pi % C::kChunks;
+                            if ((pi & 1) != half_id) continue;
+                            if (!__any_sync(0xffffffffu, f[w] != 1.0f)) continue;
+                            uint8_t* line = tile + ch * kChunkBytes + (lane + 32 * w) * 128;
+                            const float fw = f[w];
 #pragma unroll
-                            for (int b = 0; b < kBatch; ++b) {
-                                uint32_t* w32 = reinterpret_cast<uint32_t*>(&v[b]);
+                            for (int h = 0; h < 2; ++h) {
+                                uint4 v[4];
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    float lo, hi;
-                                    if constexpr (kBf16) {
-                                        lo = __uint_as_float(w32[e] << 16);
-                                        hi = __uint_as_float(w32[e] & 0xffff0000u);
-                                    } else {
-                                        const __half2 h = *reinterpret_cast<const __half2*>(&w32[e]);
-                                        lo = __low2float(h);
-                                        hi = __high2float(h);
+                                for (int b = 0; b < 4; ++b)
+                                    v[b] = *reinterpret_cast<const uint4*>(line + (((h * 4 + b) ^ (lane & 7)) << 4));
+#pragma unroll
+                                for (int b = 0; b < 4; ++b) {
+                                    uint32_t* w32 = reinterpret_cast<uint32_t*>(&v[b]);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) {
+                                        float lo, hi;
+                                        if constexpr (kBf16) {
+                                            lo = __uint_as_float(w32[e] << 16);
+                                            hi = __uint_as_float(w32[e] & 0xffff0000u);
+                                        } else {
+                                            const __half2 hh = *reinterpret_cast<const __half2*>(&w32[e]);
+                                            lo = __low2float(hh);
+                                            hi = __high2float(hh);
+                                        }
+                                        // x * f + (-0) = x * f with the sign of a zero product kept
+                                        ffma2(lo, hi, lo, hi, fw, fw, -0.0f, -0.0f);
+                                        w32[e] = pack2<kBf16>(lo, hi);
                                     }
-                                    w32[e] = pack2<kBf16>(lo * fr[b], hi * fr[b]);
                                 }
-                            }
 #pragma unroll
-                            for (int b = 0; b < kBatch; ++b) {
-                                const int it = it0 + b;
-                                const int r = ((((it & 15) << 1) + half_id) << 2) + (lane >> 3);
-                                *reinterpret_cast<uint4*>(tile + (it >> 4) * kChunkBytes + r * 128 + ((lane & 7) << 4)) = v[b];
+                                for (int b = 0; b < 4; ++b)
+                                    *reinterpret_cast<uint4*>(line + (((h * 4 + b) ^ (lane & 7)) << 4)) = v[b];
                             }
                         }
                         fence_proxy_async_smem();      // the MMA reads the tile through the async proxy
