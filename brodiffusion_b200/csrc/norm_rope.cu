@@ -139,6 +139,8 @@ template <bool kBf16, int kLpu>   // kLpu = lanes per (token, head) row = head_d
 __global__ void __launch_bounds__(256, 4) norm_rope_vec_kernel(const NormRopeArgs a, const NormRopeGrid g4) {
     constexpr int kUnroll = 6;
     constexpr int kHeadsPerStep = 32 / kLpu;
+    dependents_may_launch();
+    wait_for_prior_grid();
     int j = 0;
 #pragma unroll
     for (int i = 1; i < 4; ++i) j += (i < a.n_jobs && static_cast<int>(blockIdx.x) >= g4.block_begin[i]) ? 1 : 0;
@@ -229,12 +231,12 @@ __global__ void __launch_bounds__(256, 4) norm_rope_vec_kernel(const NormRopeArg
 template <bool kBf16>
 cudaError_t launch_vec(const NormRopeArgs& a, const NormRopeGrid& g4, int lpu, dim3 grid, cudaStream_t stream) {
     switch (lpu) {
-        case 1: norm_rope_vec_kernel<kBf16, 1><<<grid, 256, 0, stream>>>(a, g4); break;
-        case 2: norm_rope_vec_kernel<kBf16, 2><<<grid, 256, 0, stream>>>(a, g4); break;
-        case 4: norm_rope_vec_kernel<kBf16, 4><<<grid, 256, 0, stream>>>(a, g4); break;
-        case 8: norm_rope_vec_kernel<kBf16, 8><<<grid, 256, 0, stream>>>(a, g4); break;
-        case 16: norm_rope_vec_kernel<kBf16, 16><<<grid, 256, 0, stream>>>(a, g4); break;
-        default: norm_rope_vec_kernel<kBf16, 32><<<grid, 256, 0, stream>>>(a, g4); break;
+        case 1: return launch_dependent(norm_rope_vec_kernel<kBf16, 1>, grid, dim3(256), 0, stream, a, g4);
+        case 2: return launch_dependent(norm_rope_vec_kernel<kBf16, 2>, grid, dim3(256), 0, stream, a, g4);
+        case 4: return launch_dependent(norm_rope_vec_kernel<kBf16, 4>, grid, dim3(256), 0, stream, a, g4);
+        case 8: return launch_dependent(norm_rope_vec_kernel<kBf16, 8>, grid, dim3(256), 0, stream, a, g4);
+        case 16: return launch_dependent(norm_rope_vec_kernel<kBf16, 16>, grid, dim3(256), 0, stream, a, g4);
+        default: return launch_dependent(norm_rope_vec_kernel<kBf16, 32>, grid, dim3(256), 0, stream, a, g4);
     }
     return cudaGetLastError();
 }

@@ -155,6 +155,7 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     uint64_t* kv_ready = q_ready + 2;    // [ST] tile landed and, where needed, scaled (kScale)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(kv_ready + ST);
 
+    dependents_may_launch();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int head = blockIdx.y;
@@ -205,6 +206,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // barriers, tensor memory and descriptors are set up; from here on global memory is touched
+    wait_for_prior_grid();
 
     if (warp < 8) {
         // ------------------------------------------------ softmax + epilogue
@@ -779,9 +782,8 @@ cudaError_t launch_t(const SdpaLaunch& L, cudaStream_t stream) {
     if (e != cudaSuccess) return e;
     dim3 grid(static_cast<unsigned>(L.q_ctas), static_cast<unsigned>(L.num_heads),
               static_cast<unsigned>(L.batch));
-    kern<<<grid, kThreads, C::kSmemBytes, stream>>>(L.tmQ[0], L.tmQ[1], L.tmK[0], L.tmK[1], L.tmV[0],
-                                                   L.tmV[1], L.args);
-    return cudaGetLastError();
+    return launch_dependent(kern, grid, dim3(kThreads), C::kSmemBytes, stream, L.tmQ[0], L.tmQ[1], L.tmK[0],
+                            L.tmK[1], L.tmV[0], L.tmV[1], L.args);
 }
 
 template <int HD, bool kBf16>

@@ -71,6 +71,34 @@ inline int sm_count() {
     return count[dev];
 }
 
+// Programmatic dependent launch.  A kernel launched through launch_dependent() may
+// become resident while the kernel before it in the stream is still running (as that
+// one's CTAs retire, once all of them have passed dependents_may_launch()); it does
+// its set-up and then holds at wait_for_prior_grid() until the earlier grid has
+// completed and its writes are visible.  Every kernel launched this way calls
+// wait_for_prior_grid() before its first access to global memory.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+__device__ __forceinline__ void dependents_may_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void wait_for_prior_grid() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
