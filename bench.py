@@ -277,6 +277,23 @@ def measure_sana(bd, B, nh, N, steps=20, sampler=None):
     return ms, byt / (ms * 1e-3) / 1e9, n_sets, byt
 
 
+def measure_copy_same_bytes(B, nh, N, steps=20):
+    """Context for the Sana figures, not a product path: a plain device-to-device copy
+    (the library's copy kernel) that moves as many bytes as the linear attention does
+    (2 tensors' worth read, 2 written), timed the same way (CUDA-graph replay of
+    ``steps`` launches, buffers rotating over more than the L2).  Returns ms per launch."""
+    import torch
+    half = 2 * B * nh * 32 * N                 # elements read = elements written
+    n_sets = max(2, int(300e6 / (4.0 * half)) + 1)
+    src = [torch.empty(half, device="cuda", dtype=torch.bfloat16).normal_() for _ in range(n_sets)]
+    dst = [torch.empty(half, device="cuda", dtype=torch.bfloat16) for _ in range(n_sets)]
+
+    def step(i):
+        dst[i % n_sets].copy_(src[i % n_sets])
+
+    return graph_ms(step, steps)
+
+
 def measure_proj(bd, n_proj, steps=20, sampler=None):
     """Projections around the Flux 1024 px attention call (4608 tokens, 3072 ->
     3072, BF16): n_proj = 3 is one bdattn_qkv_norm_rope_fwd call, 1 is one
@@ -369,8 +386,12 @@ def other_configurations(bd):
     for name, (B, nh, N) in SANA_WORKLOADS.items():
         try:
             ms, gbs, _, _ = measure_sana(bd, B, nh, N)
+            copy_ms = measure_copy_same_bytes(B, nh, N)
             also[name] = {"ms": ms, "achieved": gbs, "unit": "GB/s", "frac": gbs / peak_gbs,
-                          "what": f"Sana ReLU linear attention, batch {B}, {nh} x 32, {N} tokens"}
+                          "what": f"Sana ReLU linear attention, batch {B}, {nh} x 32, {N} tokens",
+                          "copy_same_bytes_ms": copy_ms,
+                          "copy_same_bytes": "library device-to-device copy of as many bytes, timed the same way "
+                                             "(context: what a single streaming pass reaches at this size)"}
         except Exception as e:
             also[name] = {"error": f"{type(e).__name__}: {e}"}
     tensor("qwen_cached", lambda: measure_qwen_cached(bd, False),
