@@ -653,14 +653,11 @@ int bdattn_linear_attn_relu_fwd(const void* q, const void* k, const void* v, voi
     const int chunks = (n_tokens + 127) / 128;
     int cs = 1;
     while (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 148 && chunks >= cs * 2) cs *= 2;
-    // Long sequences: split once more and let two CTAs share an SM (three ring
-    // items each instead of eight), so that one CTA's reduction and barriers hide
-    // behind the other's streaming.  Not worth a cluster barrier on short ones.
+    // One CTA per SM (16 consumer warps, a ring of eight 16 KB items).  Splitting long
+    // sequences once more so that two 8-warp CTAs share an SM was slower at every shape
+    // tried (28.6 against 30.6 us at 4096 tokens, batch 2): it buys a cluster barrier
+    // and a second reduction where the 16 warps of one CTA already hide the latencies.
     a.stages = 8;
-    if (cs < 8 && static_cast<long long>(batch) * num_heads * cs * 2 <= 296 && chunks >= cs * 2 * 8) {
-        cs *= 2;
-        a.stages = 3;
-    }
     cudaError_t e = bdattn::launch_linear_attn(a, tq, tk, tv, to, cs, reinterpret_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return cuda_fail(op, e);
     return 0;

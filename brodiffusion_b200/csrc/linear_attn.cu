@@ -6,8 +6,9 @@
 //   out    = (S relu(Q)) / (z relu(Q) + eps)
 //
 // One thread-block cluster of CS CTAs (CS in {1, 2, 4, 8}, picked so that
-// batch * heads * CS fills the SMs) owns one (batch, head).  Each CTA streams
-// its share of the tokens twice:
+// batch * heads * CS fills the SMs; one CTA per SM) owns one (batch, head).
+// A CTA has two groups of eight consumer warps that take the ring items in
+// turn, and streams its share of the tokens twice:
 //   pass A  K and V chunks (128 tokens) -> partial [S; z] on the legacy
 //           tensor path (mma.sync m16n8k16, FP32 accumulate; the matrices are
 //           32 x 32, far below a tcgen05 tile), ReLU applied to the B
@@ -32,10 +33,14 @@ namespace {
 
 namespace cg = cooperative_groups;
 
-constexpr int kLaWarps = 8;                   // consumer warps; one more warp feeds the ring by TMA
+constexpr int kLaItemWarps = 8;               // consumer warps that work on one ring item
+constexpr int kLaWarps = 16;                  // consumer warps: two groups of 8 take the ring items in turn, so
+                                              // that twice as many independent instruction streams hide the
+                                              // latencies of a chunk; one more warp feeds the ring by TMA
 constexpr int kLaThreads = (kLaWarps + 1) * 32;
+constexpr int kLaGroups = kLaWarps / kLaItemWarps;
 constexpr int kLaChunk = 128;                 // tokens per ring item
-constexpr int kLaMaxStages = 8;               // ring of 16 KB items: 8 with one CTA per SM, 3 when two share it
+constexpr int kLaMaxStages = 8;               // ring of 16 KB items
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
 constexpr int kLaPieceBytes = 32 * 32 * 2;    // output piece of one warp and item: 32 rows x 32 tokens (64-byte rows)
@@ -92,11 +97,12 @@ __device__ __forceinline__ uint32_t swz(int row, int chunk) {
     return static_cast<uint32_t>(row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-__global__ void __launch_bounds__(kLaThreads, 2)
+__global__ void __launch_bounds__(kLaThreads, 1)
 linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmO,
                    const LinearAttnArgs a) {
     extern __shared__ uint8_t la_raw[];
+    constexpr int kGroups = kLaGroups;      // group (item mod kGroups) takes an item
     LaSmem& sm = *reinterpret_cast<LaSmem*>((reinterpret_cast<uintptr_t>(la_raw) + 1023) &
                                             ~static_cast<uintptr_t>(1023));
     cg::cluster_group cluster = cg::this_cluster();
@@ -136,7 +142,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (tid == 0) {
         for (int s = 0; s < kLaStages; ++s) {
             mbar_init(&sm.full[s], 1);
-            mbar_init(&sm.empty[s], kLaWarps);
+            mbar_init(&sm.empty[s], kLaItemWarps);
         }
         fence_mbar_init();
     }
@@ -213,10 +219,12 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) zacc[nt] = 0.0f;
 
-    const int box = warp >> 2;           // which 64-token box of the chunk
-    const int chunk0 = (warp & 3) * 2;   // first 16-byte chunk of this warp's 16 tokens
+    const int group = warp / kLaItemWarps;   // which items this warp works on
+    const int wg = warp % kLaItemWarps;      // its place among the eight warps of an item
+    const int box = wg >> 2;             // which 64-token box of the chunk
+    const int chunk0 = (wg & 3) * 2;     // first 16-byte chunk of this warp's 16 tokens
     // pass A
-    for (int it = 0; it < n_mine; ++it) {
+    for (int it = group; it < n_mine; it += kGroups) {
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
         if (ok) {
@@ -266,7 +274,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         z += __shfl_xor_sync(0xffffffffu, z, 2);
         if (q4 == 0) sm.partial[warp][32 * 32 + nt * 8 + g] = z;
     }
-    asm volatile("bar.sync 1, 256;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(kLaWarps * 32) : "memory");
     for (int i = tid; i < kLaState; i += kLaWarps * 32) {
         float s = 0.0f;
 #pragma unroll
@@ -343,27 +351,27 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                 ah[mt][ks][r] = pack2<true>(x0, x1);
             }
 
-    // Warp w owns tokens [32 w, 32 w + 32) of a 256-token item (half of box w / 2)
+    // Warp w of an item's eight owns tokens [32 w, 32 w + 32) of the 256-token item (half of box w / 2)
     // and stages and stores that piece by itself (TMA store issued by its lane 0),
     // so no barrier of the CTA sits between items and the warps drift apart, which
     // hides the latency chain of a piece (tile load, MMAs, reciprocal, packing).
     // Two pieces per warp alternate: before a piece is overwritten, the store that
     // last read it has finished reading.  The pieces lie where the partial states
     // of the reduction were: every warp is past the barrier that followed it.
-    for (int it = n_mine; it < n_items; ++it) {
+    for (int bi = group; bi < n_b; bi += kGroups) {
+        const int it = n_mine + bi;
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
-        const int bi = it - n_mine;
-        if (2 * bi + (warp >> 2) < n_mine) {          // this warp's 128-token chunk exists
-            uint8_t* stage = sm.out_stage[warp][bi & 1];
+        if (2 * bi + (wg >> 2) < n_mine) {            // this warp's 128-token chunk exists
+            uint8_t* stage = sm.out_stage[warp][(bi / kGroups) & 1];
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
             if (ok) {
-                const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (warp >> 1) * kLaBoxBytes;
+                const uint32_t qb = smem_u32(ring_base + slot * kLaSlotBytes) + (wg >> 1) * kLaBoxBytes;
 #pragma unroll
                 for (int nt = 0; nt < 4; ++nt) {
                     uint32_t b[4];
-                    ldsm_x4_trans(qb + swz(lane, (warp & 1) * 4 + nt), b[0], b[1], b[2], b[3]);
+                    ldsm_x4_trans(qb + swz(lane, (wg & 1) * 4 + nt), b[0], b[1], b[2], b[3]);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) b[i] = relu2(b[i]);
                     float o[3][4];
@@ -399,7 +407,7 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (ok && lane == 0) {
-                const int tok = (c_begin + 2 * bi) * kLaChunk + warp * 32;
+                const int tok = (c_begin + 2 * bi) * kLaChunk + wg * 32;
                 if (tok < a.n_tokens) tma_store_3d(&tmO, stage, tok, row0, batch);
                 tma_store_commit();
             }
@@ -417,9 +425,9 @@ cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, 
                                const CUtensorMap& tmV, const CUtensorMap& tmO, int cluster_size,
                                cudaStream_t stream) {
     const size_t smem = sizeof(LaSmem) + static_cast<size_t>(a.stages - 1) * kLaSlotBytes + 1024;
-    // the larger of the two ring sizes is set once per device; both launches fit under it
-    constexpr int kMaxSmem = static_cast<int>(sizeof(LaSmem) + 7 * kLaSlotBytes + 1024);
-    if (static_cast<int>(smem) > kMaxSmem) return cudaErrorInvalidValue;
+    // the largest ring is set once per device; every launch fits under it
+    constexpr int kMaxSmem = static_cast<int>(sizeof(LaSmem) + (kLaMaxStages - 1) * kLaSlotBytes + 1024);
+    if (a.stages < 1 || static_cast<int>(smem) > kMaxSmem) return cudaErrorInvalidValue;
     cudaError_t e = set_max_smem_once(linear_attn_kernel, kMaxSmem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
