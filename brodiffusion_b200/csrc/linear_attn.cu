@@ -40,7 +40,10 @@ constexpr int kLaWarps = 16;                  // consumer warps: two groups of 8
 constexpr int kLaThreads = (kLaWarps + 1) * 32;
 constexpr int kLaGroups = kLaWarps / kLaItemWarps;
 constexpr int kLaChunk = 128;                 // tokens per ring item
-constexpr int kLaMaxStages = 8;               // ring of 16 KB items
+constexpr int kLaMaxStages = 8;               // ring of 16 KB items; a multiple of the number of warp groups, so that
+                                              // a group always meets the same slots and sees every phase of their
+                                              // barriers (a ring of nine, where the groups alternate on every slot,
+                                              // ended one run with a launch failure and is refused by the launcher)
 constexpr int kLaBoxBytes = 32 * 64 * 2;      // one 64-token x 32-row box
 constexpr int kLaSlotBytes = 4 * kLaBoxBytes; // K (2 boxes) + V (2 boxes)
 constexpr int kLaPieceBytes = 32 * 32 * 2;    // output piece of one warp and item: 32 rows x 32 tokens (64-byte rows)
@@ -358,12 +361,15 @@ linear_attn_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     // Two pieces per warp alternate: before a piece is overwritten, the store that
     // last read it has finished reading.  The pieces lie where the partial states
     // of the reduction were: every warp is past the barrier that followed it.
-    for (int bi = group; bi < n_b; bi += kGroups) {
-        const int it = n_mine + bi;
+    // (an item belongs to group item mod kGroups in both passes: with a ring that is a
+    // multiple of kGroups a group always meets the same slots and every phase of their barriers)
+    int mine_b = 0;                                   // pass B items this group has taken
+    for (int it = n_mine + (group + kGroups - n_mine % kGroups) % kGroups; it < n_items; it += kGroups, ++mine_b) {
+        const int bi = it - n_mine;
         const int slot = it % kLaStages;
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&sm.full[slot], static_cast<uint32_t>((it / kLaStages) & 1)));
         if (2 * bi + (wg >> 2) < n_mine) {            // this warp's 128-token chunk exists
-            uint8_t* stage = sm.out_stage[warp][(bi / kGroups) & 1];
+            uint8_t* stage = sm.out_stage[warp][mine_b & 1];
             if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
             __syncwarp();
             if (ok) {
@@ -427,7 +433,9 @@ cudaError_t launch_linear_attn(const LinearAttnArgs& a, const CUtensorMap& tmQ, 
     const size_t smem = sizeof(LaSmem) + static_cast<size_t>(a.stages - 1) * kLaSlotBytes + 1024;
     // the largest ring is set once per device; every launch fits under it
     constexpr int kMaxSmem = static_cast<int>(sizeof(LaSmem) + (kLaMaxStages - 1) * kLaSlotBytes + 1024);
-    if (a.stages < 1 || static_cast<int>(smem) > kMaxSmem) return cudaErrorInvalidValue;
+    static_assert(kLaMaxStages % kLaGroups == 0, "every warp group must own a fixed set of ring slots");
+    if (a.stages < kLaGroups || a.stages % kLaGroups != 0 || static_cast<int>(smem) > kMaxSmem)
+        return cudaErrorInvalidValue;
     cudaError_t e = set_max_smem_once(linear_attn_kernel, kMaxSmem);
     if (e != cudaSuccess) return e;
     cudaLaunchConfig_t cfg = {};
