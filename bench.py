@@ -445,6 +445,30 @@ def library_baselines(sets, batch, L, nh_l):
 
 
 # ---------------------------------------------------------------------- ours
+def bind_host_to_gpu(local_rank):
+    """Keeps this process (and with it the pinned staging buffers it allocates from here
+    on) on the CPU cores next to its GPU, as NVML reports them, so that the uploads and
+    downloads of the end-to-end figure do not cross sockets.  Reads NVML only; a host that
+    refuses the affinity call, or an image without NVML, leaves things as they were.
+    Returns a word for the JSON line."""
+    try:
+        import pynvml
+        import torch
+        pr = torch.cuda.get_device_properties(local_rank)
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(
+            f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0".encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        near &= os.sched_getaffinity(0)
+        if not near:
+            return "unchanged (no usable cores reported next to the GPU)"
+        os.sched_setaffinity(0, near)
+        return f"{len(near)} cores next to the GPU"
+    except Exception as e:
+        return f"unchanged ({type(e).__name__})"
+
+
 def run_ours(args, rank, world, local_rank):
     import numpy as np
     import torch
@@ -454,6 +478,7 @@ def run_ours(args, rank, world, local_rank):
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    host_binding = bind_host_to_gpu(local_rank)
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -817,7 +842,7 @@ def run_ours(args, rank, world, local_rank):
             "l2_sets": f"{n_sets} input sets, {n_sets * set_bytes / 1e6:.0f} MB per rank",
             "clocks": sampler.summary(),
             "e2e": {"value": flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "ms_per_step": e2e_ms, "mode": e2e_mode,
+                    "ms_per_step": e2e_ms, "mode": e2e_mode, "host_cores": host_binding,
                     "h2d_bytes_per_step": 3 * batch * L * d_l * 2,
                     "d2h_bytes_per_step": batch * L * d_l * 2},
             "gpu_launches": launches_per_step * args.steps * args.repeats,
