@@ -233,30 +233,48 @@ gemm_tc05_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0u;
                 }
+                // the 32 bias values of this piece (and of its gate), zero where there is none
+                float bx[32], bg[kGeglu ? 32 : 1];
+                const bool whole = c + 32 <= n_valid;
+                if (p.bias != nullptr && whole) {
+                    load32_as_float<kBf16>(p.bias, n0 + c, bx);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        bx[i] = 0.0f;
+                        if (p.bias != nullptr && c + i < n_valid) {
+                            const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + c + i];
+                            bx[i] = kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                          : __half2float(*reinterpret_cast<const __half*>(&b));
+                        }
+                    }
+                }
+                if constexpr (kGeglu) {
+                    if (p.bias != nullptr && geglu && whole) {
+                        load32_as_float<kBf16>(p.bias, n0 + p.geglu_offset + c, bg);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            bg[i] = 0.0f;
+                            if (p.bias != nullptr && geglu && c + i < n_valid) {
+                                const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + p.geglu_offset + c + i];
+                                bg[i] = kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
+                                              : __half2float(*reinterpret_cast<const __half*>(&b));
+                            }
+                        }
+                    }
+                }
                 float f[32];
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    const int col = c + i;
-                    float x = __uint_as_float(v[i]);
-                    if (col < n_valid) {
-                        if (p.bias != nullptr) {
-                            const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + col];
-                            x += kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
-                                       : __half2float(*reinterpret_cast<const __half*>(&b));
-                        }
+                    float x = __uint_as_float(v[i]) + bx[i];
+                    if constexpr (kGeglu) {
                         if (geglu) {
-                            float gate = __uint_as_float(gt[i]);
-                            if (p.bias != nullptr) {
-                                const uint16_t b = reinterpret_cast<const uint16_t*>(p.bias)[n0 + p.geglu_offset + col];
-                                gate += kBf16 ? __uint_as_float(static_cast<uint32_t>(b) << 16)
-                                              : __half2float(*reinterpret_cast<const __half*>(&b));
-                            }
+                            const float gate = __uint_as_float(gt[i]) + bg[i];
                             x *= 0.5f * gate * (1.0f + erff(gate * 0.7071067811865475f));
                         }
-                    } else {
-                        x = 0.0f;
                     }
-                    f[i] = x;
+                    f[i] = c + i < n_valid ? x : 0.0f;
                 }
                 if (row < p.M) {
 #pragma unroll

@@ -374,4 +374,34 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return r;
 }
 
+// 32 consecutive 16-bit values from element i of `base` as floats: four 16-byte loads
+// when the address allows (every lane of a warp reads the same words: a broadcast), else
+// one load per value.
+template <bool kBf16>
+__device__ __forceinline__ void load32_as_float(const void* base, long long i, float (&out)[32]) {
+    const uint16_t* p = reinterpret_cast<const uint16_t*>(base) + i;
+    auto widen = [](uint32_t h) {
+        if constexpr (kBf16) return __uint_as_float(h << 16);
+        else {
+            const uint16_t b = static_cast<uint16_t>(h);
+            return __half2float(*reinterpret_cast<const __half*>(&b));
+        }
+    };
+    if ((reinterpret_cast<uintptr_t>(p) & 15u) == 0) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const uint4 w = __ldg(reinterpret_cast<const uint4*>(p) + v);
+            const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                out[v * 8 + 2 * e] = widen(ws[e] & 0xffffu);
+                out[v * 8 + 2 * e + 1] = widen(ws[e] >> 16);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) out[e] = widen(__ldg(p + e));
+    }
+}
+
 }  // namespace bdattn
