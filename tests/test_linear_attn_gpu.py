@@ -28,10 +28,11 @@ def test_golden(bd, golden):
     assert np.abs(sz[0] - g["sana_sz"]).max() < 1e-3 * np.abs(g["sana_sz"]).max()
 
 
-@pytest.mark.parametrize("N,B", [(1024, 2), (4096, 2), (1024, 1), (4096, 1)])
+@pytest.mark.parametrize("N,B", [(1024, 2), (4096, 2), (1024, 1), (4096, 1), (16384, 1)])
 def test_sana_1600m_shapes(bd, oracle, N, B):
     """Sana 1600M: 70 heads x 32, 1024 / 4096 tokens, batch 2 (CFG) and the
-    reference's own per-branch batch of 1 (which runs as a cluster of 2)."""
+    reference's own per-branch batch of 1 (which runs as a cluster of 2); 16384
+    tokens (4096 px) walks the ring a dozen times per CTA."""
     nh, hd = 70, 32
     D = nh * hd
     q = synth.activations((B, D, N), 6001 + N)
