@@ -783,13 +783,16 @@ def run_ours(args, rank, world, local_rank):
             ], nh_l, HD)
         for ci, (r0, r1) in enumerate(chunks):
             cur.wait_event(ev_q[ci])
-            pp = None
-            if gathered is not None:
-                pp = [gathered.peer_ptrs(r0)]
+            pp, mp = None, None
+            if gathered is not None:                 # the same gather form as the timed region
+                if mc_ptrs is not None:
+                    mp = [gathered.multicast_ptr(r0)]
+                else:
+                    pp = [gathered.peer_ptrs(r0)]
             bd.sdpa_fwd(Bf["q"][:, r0:r1], [Bf["kr"][:, :txt], Bf["kr"][:, txt:]],
                         [Bf["v"][:, :txt], Bf["v"][:, txt:]], Bf["o"][:, r0:r1], nh_l,
                         q_norm=dict(gain=gains[2] if r0 < txt else gains[0], cos=cos, sin=sin, rope_row0=r0),
-                        peer_out_ptrs=pp)
+                        peer_out_ptrs=pp, multicast_out_ptrs=mp)
             ev_o = torch.cuda.Event()
             ev_o.record(cur)
             s_out.wait_event(ev_o)
