@@ -116,28 +116,6 @@ __device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, 
         : "=f"(d0), "=f"(d1)
         : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
-// 2^x for a pair on the FMA pipe instead of the MUFU: round to the nearest integer with
-// the 1.5 * 2^23 trick, degree-3 polynomial of the remainder in [-0.5, 0.5] (relative
-// error 7.5e-5, a thirtieth of the rounding of P to 16 bits), exponent added to the bits
-// of the polynomial.  A pair costs about as many FMA-pipe cycles as MUFU cycles, so it
-// only pays where the exponentials bound the step and the FMA pipe has room: at head_dim
-// 64 (short MMAs, the two query tiles' softmax phases overlap) one pair in four gives 3 %
-// (59.8 -> 58.0 us on 4096 x 8 x 64, 187.3 -> 180.6 us on 4352 x 24 x 64); at head_dim 128
-// every share tried was slower (1166 -> 1135 TFLOP/s at one in four) and none is used.
-__device__ __forceinline__ void exp2_pair_fma(float& p0, float& p1, float x0, float x1) {
-    constexpr float kMagic = 12582912.0f;
-    x0 = fmaxf(x0, -125.0f);
-    x1 = fmaxf(x1, -125.0f);
-    float t0, t1, r0, r1, f0, f1, q0, q1;
-    fadd2(t0, t1, x0, x1, kMagic, kMagic);
-    fadd2(r0, r1, t0, t1, -kMagic, -kMagic);
-    ffma2(f0, f1, r0, r1, -1.0f, -1.0f, x0, x1);
-    ffma2(q0, q1, f0, f1, 0.0551716685295105f, 0.0551716685295105f, 0.2426111251115799f, 0.2426111251115799f);
-    ffma2(q0, q1, q0, q1, f0, f1, 0.6932609677314758f, 0.6932609677314758f);
-    ffma2(q0, q1, q0, q1, f0, f1, 0.9999280571937561f, 0.9999280571937561f);
-    p0 = __uint_as_float(__float_as_uint(q0) + (__float_as_uint(t0) << 23));
-    p1 = __uint_as_float(__float_as_uint(q1) + (__float_as_uint(t1) << 23));
-}
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
@@ -475,12 +453,8 @@ sdpa_tc05_kernel(const __grid_constant__ CUtensorMap tmQ0, const __grid_constant
                     const int c0 = ch * 32 + 2 * i;
                     float x0, x1, p0, p1;
                     ffma2(x0, x1, s[c0], s[c0 + 1], sl2, sl2, neg_ms, neg_ms);
-                    if (kHooks == 0 && HD == 64 && (i & 3) == 3) {
-                        exp2_pair_fma(p0, p1, x0, x1);      // every fourth pair, head_dim 64 only (see there)
-                    } else {
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
-                    }
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
                     fadd2(rs[2 * (i & 3)], rs[2 * (i & 3) + 1], rs[2 * (i & 3)], rs[2 * (i & 3) + 1], p0, p1);
                     pk[i] = pack2<kBf16>(p0, p1);
                 }

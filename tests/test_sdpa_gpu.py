@@ -465,15 +465,18 @@ def test_all_keys_masked_gives_zeros(bd, hd):
     assert np.all(out == 0.0)
 
 
-def test_causal_with_more_queries_than_keys(bd, oracle):
-    """q_offset < 0: the first queries see no key at all and must give 0."""
-    nh, hd = 2, 128
+@pytest.mark.parametrize("hd", [128, 64, 40])
+def test_causal_with_more_queries_than_keys(bd, oracle, hd):
+    """q_offset < 0: the first queries see no key at all and must give 0 (every
+    exponential of such a row must be exactly zero, whichever way it is computed)."""
+    nh = 2
     q = synth.activations((300, nh * hd), 4501)
     k = synth.activations((200, nh * hd), 4502)
     v = synth.activations((200, nh * hd), 4503)
     out = G.sdpa(bd, q, k, v, nh, mask_mode=bd.MASK_CAUSAL)
     ref = oracle.sdpa(q, k, v, nh, mask_mode=1)
     assert np.all(ref[:100] == 0.0)
+    assert np.all(out[:100] == 0.0)
     G.check(out, ref, what="negative q_offset")
 
 
